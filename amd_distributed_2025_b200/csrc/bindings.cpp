@@ -1,0 +1,274 @@
+// Python bindings: torch tensors in, raw pointers + current CUDA stream out.
+//
+// Plays the role of the reference's CPP_WRAPPER / torch::Tensor wrapper pairs
+// (all2all/hipv8.py:20-40,229-237), with host-side validation of dtypes, shapes and
+// contiguity and launches on the caller's current stream instead of the default stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "gemm_rs.h"
+#include "moe.h"
+#include "status.h"
+#include "symm_heap.h"
+
+namespace py = pybind11;
+using b200::SymmHeap;
+
+namespace {
+
+void cuda_check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kHalf: return 0;
+    case at::kBFloat16: return 1;
+    case at::kFloat: return 2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t, " (expected float16, bfloat16 or float32)");
+  }
+  return -1;
+}
+
+void fill_peer_bases(const SymmHeap& heap, uint64_t* out) {
+  for (int r = 0; r < b200::kMaxWorldSize; ++r) out[r] = r < heap.world_size() ? heap.peer_base(r) : 0;
+}
+
+py::dict status_to_dict(const b200::StatusWord& w) {
+  py::dict d;
+  d["code"] = w.code;
+  d["phase"] = w.phase;
+  d["peer"] = w.peer;
+  d["detail"] = w.detail;
+  d["epoch"] = w.epoch;
+  d["seen"] = w.seen;
+  return d;
+}
+
+at::Tensor heap_view(SymmHeap& heap, int64_t offset, std::vector<int64_t> shape, at::ScalarType dtype) {
+  int64_t numel = 1;
+  for (auto s : shape) numel *= s;
+  const int64_t nbytes = numel * (int64_t)c10::elementSize(dtype);
+  TORCH_CHECK(offset >= 0 && (uint64_t)(offset + nbytes) <= heap.bytes(), "heap view [", offset, ", ",
+              offset + nbytes, ") exceeds the slab of ", heap.bytes(), " bytes");
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, heap.device());
+  return at::from_blob(static_cast<uint8_t*>(heap.local_base()) + offset, shape, opts);
+}
+
+// ----------------------------------------------------------------------------- MoE ----
+
+void moe_dispatch(SymmHeap& heap, const at::Tensor& x, const at::Tensor& indices, int64_t num_experts,
+                  int64_t max_recv, int64_t off_counts, int64_t off_expert_x, int64_t off_expert_meta,
+                  at::Tensor blk_hist, at::Tensor local_rank, at::Tensor route, at::Tensor expert_num_tokens,
+                  int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous(), "x must be a contiguous [T, H] CUDA tensor");
+  TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() && indices.scalar_type() == at::kInt,
+              "indices must be a contiguous [T, k] int32 CUDA tensor");
+  TORCH_CHECK(indices.size(0) == x.size(0), "x and indices disagree on the token count");
+  TORCH_CHECK(x.get_device() == heap.device(), "x is not on the heap's device");
+  const int ws = heap.world_size();
+  TORCH_CHECK(num_experts % ws == 0, "num_experts must be divisible by world_size");
+  const int64_t T = x.size(0), k = indices.size(1), n = T * k;
+  const int64_t e_local = num_experts / ws;
+  TORCH_CHECK(e_local * max_recv < (1ll << 31), "expert buffer has too many rows for 32-bit row ids");
+  TORCH_CHECK(n < (1ll << 31), "too many (token, k) entries");
+
+  c10::cuda::CUDAGuard guard(heap.device());
+  const int max_blocks = b200::moe_dispatch_max_blocks(heap.device());
+  int64_t chunk = (n + max_blocks - 1) / max_blocks;
+  if (chunk < 32) chunk = 32;
+  const int64_t count_blocks = (n + chunk - 1) / chunk;
+  int grid = max_blocks;
+  // Small problems: fewer CTAs make the in-GPU barrier cheaper; keep enough warps (8 per
+  // CTA) to move all rows at once and at least one CTA per rank for the count broadcast.
+  const int64_t want = std::max<int64_t>(std::max<int64_t>(count_blocks, (n + 7) / 8), std::min<int64_t>(ws, max_blocks));
+  if (want < grid) grid = (int)std::max<int64_t>(want, 1);
+
+  TORCH_CHECK(blk_hist.scalar_type() == at::kInt && blk_hist.is_contiguous() &&
+                  blk_hist.numel() >= std::max<int64_t>(count_blocks, 1) * num_experts,
+              "blk_hist scratch too small");
+  TORCH_CHECK(local_rank.scalar_type() == at::kInt && local_rank.is_contiguous() && local_rank.numel() >= n,
+              "local_rank scratch too small");
+  TORCH_CHECK(route.scalar_type() == at::kInt && route.is_contiguous() && route.numel() >= 2 * n,
+              "route must hold 2 int32 per (token, k) entry");
+  TORCH_CHECK(expert_num_tokens.scalar_type() == at::kInt && expert_num_tokens.numel() >= e_local,
+              "expert_num_tokens too small");
+
+  b200::MoeDispatchParams p;
+  p.x = x.data_ptr();
+  p.indices = indices.data_ptr<int32_t>();
+  p.num_tokens = (int32_t)T;
+  p.k = (int32_t)k;
+  p.num_experts = (int32_t)num_experts;
+  p.num_local_experts = (int32_t)e_local;
+  p.world_size = ws;
+  p.rank = heap.rank();
+  p.max_recv = (int32_t)max_recv;
+  p.row_bytes = (uint32_t)(x.size(1) * x.element_size());
+  p.epoch = (uint64_t)epoch;
+  p.timeout_ns = (uint64_t)timeout_ns;
+  fill_peer_bases(heap, p.peer_base);
+  p.layout.off_counts = (uint64_t)off_counts;
+  p.layout.off_expert_x = (uint64_t)off_expert_x;
+  p.layout.off_expert_meta = (uint64_t)off_expert_meta;
+  p.layout.off_expert_y = 0;
+  p.blk_hist = blk_hist.data_ptr<int32_t>();
+  p.local_rank = local_rank.data_ptr<int32_t>();
+  p.route = reinterpret_cast<int2*>(route.data_ptr<int32_t>());
+  p.expert_num_tokens = expert_num_tokens.data_ptr<int32_t>();
+  p.sync_counters = heap.sync_counters();
+  p.status = heap.status_device();
+  p.count_blocks = (int32_t)count_blocks;
+  p.chunk = (int32_t)chunk;
+  cuda_check(b200::launch_moe_dispatch(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dispatch launch");
+}
+
+void moe_expert_scale(const at::Tensor& expert_x, at::Tensor expert_y, const at::Tensor& expert_num_tokens,
+                      double scale) {
+  TORCH_CHECK(expert_x.dim() == 3 && expert_y.sizes() == expert_x.sizes(), "expert_x / expert_y shapes differ");
+  TORCH_CHECK(expert_x.is_contiguous() && expert_y.is_contiguous(), "expert buffers must be contiguous");
+  c10::cuda::CUDAGuard guard(expert_x.device());
+  cuda_check(b200::launch_moe_expert_scale(expert_x.data_ptr(), expert_y.data_ptr(),
+                                           expert_num_tokens.data_ptr<int32_t>(), (int)expert_x.size(0),
+                                           (int)expert_x.size(1), (int)expert_x.size(2),
+                                           dtype_code(expert_x.scalar_type()), dtype_code(expert_y.scalar_type()),
+                                           (float)scale, at::cuda::getCurrentCUDAStream()),
+             "moe_expert_scale launch");
+}
+
+void moe_combine(SymmHeap& heap, at::Tensor out, const at::Tensor& weights, const at::Tensor& route,
+                 int64_t num_tokens, int64_t max_recv, int64_t off_expert_y, int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.is_contiguous(), "out must be a contiguous [T, H] CUDA tensor");
+  TORCH_CHECK(weights.scalar_type() == at::kFloat && weights.is_contiguous() && weights.dim() == 2,
+              "weights must be contiguous fp32 [T, k]");
+  TORCH_CHECK(out.size(0) >= num_tokens && weights.size(0) >= num_tokens, "out/weights have fewer rows than tokens");
+  const int64_t k = weights.size(1);
+  TORCH_CHECK(route.scalar_type() == at::kInt && route.numel() >= 2 * num_tokens * k, "route too small");
+  c10::cuda::CUDAGuard guard(heap.device());
+  b200::MoeCombineParams p;
+  p.out = out.data_ptr();
+  p.weights = weights.data_ptr<float>();
+  p.route = reinterpret_cast<const int2*>(route.data_ptr<int32_t>());
+  p.num_tokens = (int32_t)num_tokens;
+  p.k = (int32_t)k;
+  p.hidden = (int32_t)out.size(1);
+  p.world_size = heap.world_size();
+  p.rank = heap.rank();
+  p.max_recv = (int32_t)max_recv;
+  p.dtype = dtype_code(out.scalar_type());
+  p.epoch = (uint64_t)epoch;
+  p.timeout_ns = (uint64_t)timeout_ns;
+  fill_peer_bases(heap, p.peer_base);
+  p.off_expert_y = (uint64_t)off_expert_y;
+  p.status = heap.status_device();
+  cuda_check(b200::launch_moe_combine(p, at::cuda::getCurrentCUDAStream()), "moe_combine launch");
+}
+
+// ------------------------------------------------------------------------- GEMM-RS ----
+
+void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+             at::Tensor out, double bias_scale, int64_t off_stage, int64_t off_counters, int64_t epoch,
+             int64_t timeout_ns, int64_t max_ctas, int64_t block_n) {
+  TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
+              "input and weight must be bf16 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "input [M, K] and weight [N, K] disagree on K");
+  TORCH_CHECK(a.is_contiguous() && w.is_contiguous() && out.is_contiguous(), "operands must be contiguous");
+  const int ws = heap.world_size();
+  const int64_t M = a.size(0), N = w.size(0), K = a.size(1);
+  TORCH_CHECK(M % ws == 0, "M must be divisible by world_size");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == M / ws && out.size(1) == N, "out must be bf16 [M/ws, N]");
+  TORCH_CHECK(K % 8 == 0, "K per rank must be a multiple of 8 (16-byte rows for TMA)");
+  TORCH_CHECK(N % 8 == 0, "N must be a multiple of 8 (16-byte vector epilogue)");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "bias must be bf16 [N]");
+    bias_ptr = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(heap.device());
+  b200::GemmRsArgs g;
+  g.a = a.data_ptr();
+  g.w = w.data_ptr();
+  g.bias = bias_ptr;
+  g.out = out.data_ptr();
+  g.M = (int)M;
+  g.N = (int)N;
+  g.K = (int)K;
+  g.world_size = ws;
+  g.rank = heap.rank();
+  g.bias_scale = (float)bias_scale;
+  fill_peer_bases(heap, g.peer_base);
+  g.off_stage = (uint64_t)off_stage;
+  g.off_counters = (uint64_t)off_counters;
+  g.epoch = (uint64_t)epoch;
+  g.timeout_ns = (uint64_t)timeout_ns;
+  g.status = heap.status_device();
+  g.sync_counters = heap.sync_counters() + 8;
+  g.max_ctas = (int)max_ctas;
+  g.block_n = (int)block_n;
+  cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "B200 (sm_100a) kernels and symmetric-memory runtime";
+  m.attr("MAX_WORLD_SIZE") = b200::kMaxWorldSize;
+  m.attr("HEAP_HEADER_BYTES") = (int64_t)b200::kHeapHeaderBytes;
+  m.attr("GEMM_RS_BLOCK_M") = b200::kGemmRsBlockM;
+  m.attr("GEMM_RS_BLOCK_N") = b200::kGemmRsBlockN;
+
+  py::class_<SymmHeap, std::shared_ptr<SymmHeap>>(m, "SymmHeap")
+      .def(py::init([](int rank, int world_size, int64_t bytes, int device) {
+             return std::make_shared<SymmHeap>(rank, world_size, (uint64_t)bytes, device);
+           }),
+           py::arg("rank"), py::arg("world_size"), py::arg("bytes"), py::arg("device"))
+      .def("ipc_handle", [](const SymmHeap& h) { return py::bytes(h.ipc_handle()); })
+      .def("open_peers",
+           [](SymmHeap& h, const std::vector<py::bytes>& handles) {
+             std::vector<std::string> hs;
+             for (const auto& b : handles) hs.push_back(std::string(b));
+             h.open_peers(hs);
+           })
+      .def("close", &SymmHeap::close)
+      .def_property_readonly("rank", &SymmHeap::rank)
+      .def_property_readonly("world_size", &SymmHeap::world_size)
+      .def_property_readonly("device", &SymmHeap::device)
+      .def_property_readonly("bytes", [](const SymmHeap& h) { return (int64_t)h.bytes(); })
+      .def_property_readonly("peers_open", &SymmHeap::peers_open)
+      .def("peer_base", [](const SymmHeap& h, int r) { return (int64_t)h.peer_base(r); })
+      .def("view", &heap_view, py::arg("offset"), py::arg("shape"), py::arg("dtype"))
+      .def("status", [](const SymmHeap& h) { return status_to_dict(h.status_host()); })
+      .def("status_sync", [](const SymmHeap& h) { return status_to_dict(h.status_sync()); })
+      .def("reset_status", &SymmHeap::reset_status)
+      .def("barrier",
+           [](SymmHeap& h, int64_t epoch, int64_t timeout_ns) {
+             c10::cuda::CUDAGuard guard(h.device());
+             cuda_check(b200::launch_symm_barrier(h, (uint64_t)epoch, (uint64_t)timeout_ns,
+                                                  at::cuda::getCurrentCUDAStream()),
+                        "barrier launch");
+           })
+      .def("wait_selftest", [](SymmHeap& h, int slot, int64_t want, int64_t timeout_ns) {
+        c10::cuda::CUDAGuard guard(h.device());
+        cuda_check(b200::launch_wait_selftest(h, slot, (uint64_t)want, (uint64_t)timeout_ns,
+                                              at::cuda::getCurrentCUDAStream()),
+                   "wait_selftest launch");
+      });
+
+  m.def("moe_dispatch", &moe_dispatch);
+  m.def("moe_expert_scale", &moe_expert_scale);
+  m.def("moe_combine", &moe_combine);
+  m.def("gemm_rs", &gemm_rs);
+  m.def("gemm_rs_workspace_bytes", [](int64_t M, int64_t N, int64_t ws) {
+    return py::make_tuple((int64_t)b200::gemm_rs_stage_bytes((int)M, (int)N, (int)ws),
+                          (int64_t)b200::gemm_rs_counter_bytes((int)M, (int)N, (int)ws));
+  });
+}

@@ -1,0 +1,53 @@
+// Row-parallel GEMM (+bias) fused with reduce-scatter, for sm_100a.
+//
+// Capability: gemm-rs/reference.py:36-60 -- every rank holds input[M, K/ws] and
+// weight[N, K/ws], the result is sum_r input_r * weight_r^T (+ bias) scattered along M so
+// that rank r keeps rows [r*M/ws, (r+1)*M/ws).  The reference runs three serial stages
+// (library GEMM, elementwise bias, library reduce-scatter).  Here ONE persistent kernel
+//   * computes 128 x BN output tiles with tcgen05.mma (bf16 in, fp32 accumulators in
+//     tensor memory), operands staged by TMA into 128B-swizzled shared memory through an
+//     mbarrier pipeline, two accumulator buffers so the epilogue of a tile overlaps the
+//     main loop of the next;
+//   * in the epilogue rounds each partial row to bf16 (the reference's rounding point)
+//     and stores it into the *owning* rank's staging slot over NVLink, then bumps that
+//     owner's arrival counter for the tile -- tiles are visited so that the rows a rank
+//     owns itself come last;
+//   * finally reduces the world_size partials of its own rows in fixed rank order in
+//     fp32, adds the bias once with its multiplicity, rounds once and writes out[M/ws, N].
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "status.h"
+
+namespace b200 {
+
+constexpr int kGemmRsBlockM = 128;
+constexpr int kGemmRsBlockN = 256;  // widest tile; narrower instantiations exist for small problems
+constexpr int kGemmRsBlockK = 64;
+
+struct GemmRsArgs {
+  const void* a;     // [M, K] bf16, row-major (this rank's K slice)
+  const void* w;     // [N, K] bf16, row-major
+  const void* bias;  // [N] bf16 or nullptr
+  void* out;         // [M / world_size, N] bf16
+  int M, N, K, world_size, rank;
+  float bias_scale;  // world_size to match the reference checker, 1 to add the bias once
+  uint64_t peer_base[kMaxWorldSize];
+  uint64_t off_stage;     // staging buffer of the current parity: bf16 [world][M/ws][N]
+  uint64_t off_counters;  // arrival counters of the current parity: uint32 [m_tiles][n_tiles]
+  uint64_t epoch;
+  uint64_t timeout_ns;
+  StatusBlock* status;
+  uint32_t* sync_counters;
+  int max_ctas;  // 0 = one per SM
+  int block_n;   // 0 = choose from the shape; else 64, 128 or 256
+};
+
+// Bytes of ONE parity of the staging buffer / the counters for a problem.
+uint64_t gemm_rs_stage_bytes(int M, int N, int world_size);
+uint64_t gemm_rs_counter_bytes(int M, int N, int world_size);
+
+cudaError_t launch_gemm_rs(const GemmRsArgs& args, cudaStream_t stream);
+
+}  // namespace b200

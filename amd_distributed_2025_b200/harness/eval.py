@@ -1,0 +1,265 @@
+"""Evaluator: runs the task's test and benchmark shape lists on N ranks.
+
+The reference names an evaluator (``eval.py``) and helpers that are not part of its tree
+(all2all/task.yml:6-8, gemm-rs/task.yml:6-8); this module supplies that role.  For every
+shape it builds the inputs on every rank (``generate_input``), calls the entry point under
+test, checks the result with the task's tolerance against the communication-free oracle,
+and in benchmark mode times it with CUDA events, maximum over ranks, and ranks the run by
+the geometric mean over shapes (all2all/task.yml:68, gemm-rs/task.yml:62).
+
+Usage::
+
+    python -m amd_distributed_2025_b200.harness.eval --task all2all --mode test --world-size 8
+    torchrun --nproc-per-node 8 -m amd_distributed_2025_b200.harness.eval --task gemm_rs --mode benchmark
+
+Without ``RANK`` in the environment the module spawns the ranks itself.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import sys
+import traceback
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from .. import contract, oracle
+from ..utils import timing
+
+
+# --------------------------------------------------------------------------------------
+# process plumbing
+# --------------------------------------------------------------------------------------
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def init_process_group(rank: int, world_size: int, backend: str, port: int, timeout_s: float = 600.0) -> None:
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    kwargs: Dict[str, Any] = {}
+    if backend == "nccl":
+        torch.cuda.set_device(rank % max(torch.cuda.device_count(), 1))
+        kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group(
+        backend, rank=rank, world_size=world_size, timeout=datetime.timedelta(seconds=timeout_s), **kwargs
+    )
+
+
+def _worker(rank: int, world_size: int, backend: str, port: int, fn: Callable, args: tuple, result_dir: str) -> None:
+    out: Dict[str, Any] = {"rank": rank, "ok": False}
+    try:
+        init_process_group(rank, world_size, backend, port)
+        out["result"] = fn(rank, world_size, *args)
+        out["ok"] = True
+    except Exception:  # noqa: BLE001 - the parent re-raises with the traceback text
+        out["error"] = traceback.format_exc()
+    finally:
+        with open(os.path.join(result_dir, f"rank{rank}.json"), "w", encoding="utf-8") as fh:
+            json.dump(out, fh)
+        if dist.is_initialized():
+            try:
+                dist.destroy_process_group()
+            except Exception:  # noqa: BLE001
+                pass
+
+
+def run_ranks(fn: Callable, world_size: int, backend: str = "gloo", args: tuple = (), timeout_s: float = 600.0) -> List[Any]:
+    """Run ``fn(rank, world_size, *args)`` on ``world_size`` fresh processes and return the
+    per-rank results (which must be JSON-serialisable).  Raises if any rank failed."""
+    import tempfile
+
+    port = free_port()
+    with tempfile.TemporaryDirectory() as tmp:
+        ctx = mp.get_context("spawn")
+        procs = [
+            ctx.Process(target=_worker, args=(r, world_size, backend, port, fn, args, tmp)) for r in range(world_size)
+        ]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout_s)
+        hung = [p for p in procs if p.is_alive()]
+        for p in hung:
+            p.kill()
+        results = []
+        for r in range(world_size):
+            path = os.path.join(tmp, f"rank{r}.json")
+            if not os.path.exists(path):
+                raise RuntimeError(f"rank {r} produced no result (exit code {procs[r].exitcode}, hung={procs[r] in hung})")
+            with open(path, "r", encoding="utf-8") as fh:
+                results.append(json.load(fh))
+    errors = [f"rank {r['rank']}:\n{r['error']}" for r in results if not r["ok"]]
+    if errors:
+        raise RuntimeError("\n".join(errors))
+    return [r["result"] for r in results]
+
+
+# --------------------------------------------------------------------------------------
+# per-task evaluation
+# --------------------------------------------------------------------------------------
+
+def _device_for(rank: int) -> torch.device:
+    if torch.cuda.is_available():
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
+
+
+def moe_rank_data(spec: Dict[str, Any], rank: int, world_size: int, device: torch.device):
+    """Input tuple of one rank.  Shapes from the task lists use the reference generator;
+    shapes that fix ``tokens_per_rank`` use the benchmark factory."""
+    if "tokens_per_rank" not in spec:
+        return contract.generate_moe_input(
+            spec["num_experts"], spec["experts_per_token"], spec["hidden_dim"], spec["max_num_tokens"],
+            spec["seed"], rank, world_size, device=device,
+        )
+    return contract.make_moe_inputs(
+        spec["num_experts"], spec["experts_per_token"], spec["hidden_dim"],
+        spec.get("max_num_tokens", spec["tokens_per_rank"]),
+        spec["seed"], rank, world_size, device=device,
+        dtype=getattr(torch, spec.get("dtype", "float16")),
+        fixed_num_tokens=spec["tokens_per_rank"],
+        routing=spec.get("routing", "uniform"), weights=spec.get("weights", "rand"),
+        zipf_s=spec.get("zipf_s", 1.2),
+    )
+
+
+def eval_moe_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, mode: str,
+                   warmup: int = 3, iters: int = 10) -> Dict[str, Any]:
+    from ..models import moe_all2all
+    from ..parallel import baseline_nccl
+
+    device = _device_for(rank)
+    cfg, mine, _, _ = moe_rank_data(spec, rank, world_size, device)
+    data = (cfg, mine, rank, world_size)
+    fn = {
+        "ours": lambda: moe_all2all.custom_kernel(data),
+        "torch": lambda: baseline_nccl.moe_torch(data),
+    }[impl]
+    out = fn()
+    expected = oracle.moe_expected_output(cfg, mine, world_size, emulate_reference_rounding=True)
+    ok, msg = oracle.check_moe_output(out, expected)
+    res: Dict[str, Any] = {"spec": spec, "ok": bool(ok), "msg": msg, "num_tokens": mine.num_tokens}
+    if impl == "ours" and device.type == "cuda":
+        layer = moe_all2all.get_layer(cfg, rank, world_size)
+        try:
+            layer.check(sync=True)
+        except Exception as exc:  # noqa: BLE001
+            res["ok"], res["msg"] = False, str(exc)
+    if mode == "benchmark" and device.type == "cuda":
+        times = timing.time_cuda(fn, warmup=warmup, iters=iters, flush=True, barrier=dist.barrier if world_size > 1 else None)
+        times = timing.max_over_ranks(times)
+        res["time_us"] = timing.summarize(times)["mean_ms"] * 1e3
+        res["median_us"] = timing.summarize(times)["median_ms"] * 1e3
+    return res
+
+
+def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, mode: str,
+                       warmup: int = 3, iters: int = 10) -> Dict[str, Any]:
+    from ..models import gemm_rs
+    from ..parallel import baseline_nccl
+
+    device = _device_for(rank)
+    dist_kind = spec.get("dist", "reference")
+    everyone = [
+        contract.make_gemm_rs_inputs(r, world_size, spec["m"], spec["n"], spec["k"], spec["has_bias"], spec["seed"],
+                                     device=device, dist=dist_kind)
+        for r in range(world_size)
+    ]
+    data = everyone[rank]
+    fn = {
+        "ours": lambda: gemm_rs.custom_kernel(data),
+        "torch": lambda: baseline_nccl.gemm_rs_torch(data),
+    }[impl]
+    out = fn()
+    truth = oracle.gemm_rs_truth([d[0] for d in everyone], [d[1] for d in everyone], data[2], rank,
+                                 dtype=torch.float32 if device.type == "cuda" else torch.float64)
+    ok, msg = oracle.check_gemm_rs_output(out, truth.to(out.dtype))
+    rel = oracle.relative_error(out, truth)
+    res: Dict[str, Any] = {"spec": spec, "ok": bool(ok and rel < 2e-2), "msg": msg, "rel_err": rel}
+    if mode == "benchmark" and device.type == "cuda":
+        times = timing.time_cuda(fn, warmup=warmup, iters=iters, flush=True, barrier=dist.barrier if world_size > 1 else None)
+        times = timing.max_over_ranks(times)
+        res["time_us"] = timing.summarize(times)["mean_ms"] * 1e3
+        res["median_us"] = timing.summarize(times)["median_ms"] * 1e3
+    return res
+
+
+def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup: int, iters: int) -> List[Dict[str, Any]]:
+    specs = contract.task_specs(task, "tests" if mode == "test" else "benchmarks")
+    results = []
+    for spec in specs:
+        spec = dict(spec)
+        spec.pop("world_size", None)  # the list is written for 8 ranks; run on what we have
+        if task == "all2all":
+            if spec["num_experts"] % world_size:
+                continue
+            results.append(eval_moe_shape(rank, world_size, spec, impl, mode, warmup, iters))
+        else:
+            if spec["m"] % world_size or spec["k"] % world_size:
+                continue
+            results.append(eval_gemm_rs_shape(rank, world_size, spec, impl, mode, warmup, iters))
+    return results
+
+
+def summarize_results(results: List[Dict[str, Any]]) -> Dict[str, Any]:
+    passed = sum(1 for r in results if r["ok"])
+    out: Dict[str, Any] = {"shapes": len(results), "passed": passed}
+    times = [r["time_us"] for r in results if "time_us" in r]
+    if times:
+        out["geomean_us"] = timing.geomean(times)
+    return out
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--task", choices=["all2all", "gemm_rs"], required=True)
+    ap.add_argument("--mode", choices=["test", "benchmark"], default="test")
+    ap.add_argument("--impl", choices=["ours", "torch"], default="ours")
+    ap.add_argument("--world-size", type=int, default=None)
+    ap.add_argument("--backend", default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default=None, help="write per-shape results to this file (rank 0)")
+    args = ap.parse_args(argv)
+
+    backend = args.backend or ("nccl" if torch.cuda.is_available() else "gloo")
+    if "RANK" in os.environ:
+        rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        if backend == "nccl":
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dist.init_process_group(backend)
+        results = run_task(rank, ws, args.task, args.mode, args.impl, args.warmup, args.iters)
+        dist.barrier()
+        dist.destroy_process_group()
+        per_rank = [results]
+        if rank != 0:
+            return 0
+    else:
+        ws = args.world_size or (torch.cuda.device_count() if torch.cuda.is_available() else 2)
+        per_rank = run_ranks(run_task, ws, backend, (args.task, args.mode, args.impl, args.warmup, args.iters), 3600.0)
+    results = per_rank[0]
+    for i, r in enumerate(results):
+        r["ok"] = all(pr[i]["ok"] for pr in per_rank)
+        line = {k: v for k, v in r.items() if k != "msg" or v}
+        print(json.dumps(line))
+    summary = summarize_results(results)
+    print(json.dumps({"task": args.task, "mode": args.mode, "impl": args.impl, "world_size": ws, **summary}))
+    if args.json:
+        with open(args.json, "w", encoding="utf-8") as fh:
+            json.dump({"results": results, "summary": summary}, fh, indent=1)
+    return 0 if summary["passed"] == summary["shapes"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

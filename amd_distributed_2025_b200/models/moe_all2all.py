@@ -1,0 +1,239 @@
+"""MoE expert-parallel layer: dispatch -> expert op -> combine over NVLink peer memory.
+
+Same contract as the reference solution (all2all/hipv8.py:254-394, oracle
+all2all/reference.py:55-272):
+
+* ``MoEAllToAll(cfg, rank, world_size)`` with
+  ``dispatch(dp_x, indices) -> (expert_num_tokens, expert_x, expert_meta)`` and
+  ``combine(out_tokens, weights, expert_meta, expert_y, expert_num_tokens, num_tokens)``;
+* ``custom_kernel((cfg, rank_data, rank, world_size)) -> y[num_tokens, hidden]``.
+
+Differences in mechanism, not in results: the three returned tensors are views of this
+rank's symmetric workspace that the *senders* filled directly (csrc/moe_kernels.cu), in
+the reference's row order (source rank, token, k); combine pulls expert outputs from the
+owners' workspaces using the route table that dispatch recorded, so no metadata or
+counts travel back.  Nothing in a call synchronises with the host.
+
+On CPU tensors (or ``backend="torch"``) the layer falls back to the library-collective
+implementation in ``parallel/baseline_nccl.py``; that is how the fp32 two-rank CPU
+configuration runs.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..contract import META_DIM, MoEConfig, MoEInput
+from ..parallel.baseline_nccl import TorchAllToAll
+from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace
+
+_DTYPE_SIZE = {torch.float16: 2, torch.bfloat16: 2, torch.float32: 4}
+
+
+def moe_slab_layout(cfg: MoEConfig, world_size: int, header_bytes: int) -> SlabLayout:
+    """Offsets of the MoE regions inside every rank's slab."""
+    e_local = cfg.num_local_experts(world_size)
+    max_recv = cfg.max_recv(world_size)
+    rows = e_local * max_recv
+    lay = SlabLayout(header_bytes)
+    lay.add("counts", world_size * cfg.num_experts * 4)
+    lay.add("expert_meta", rows * META_DIM * 4)
+    lay.add("expert_x", rows * cfg.hidden_dim * _DTYPE_SIZE[cfg.in_dtype])
+    lay.add("expert_y", rows * cfg.hidden_dim * _DTYPE_SIZE[cfg.out_dtype])
+    return lay
+
+
+class MoEAllToAll:
+    META_DIM = META_DIM
+
+    def __init__(
+        self,
+        cfg: MoEConfig,
+        rank: int,
+        world_size: int,
+        group=None,
+        device: Optional[torch.device] = None,
+        wait_limit_ms: Optional[float] = None,
+    ):
+        if cfg.in_dtype not in _DTYPE_SIZE or cfg.out_dtype not in _DTYPE_SIZE:
+            raise ValueError("in_dtype / out_dtype must be float16, bfloat16 or float32")
+        self.cfg = cfg
+        self.rank = rank
+        self.world_size = world_size
+        self.group = group
+        self.num_local_experts = cfg.num_local_experts(world_size)
+        self.max_recv = cfg.max_recv(world_size)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+
+        from ..ops import _ext
+
+        ext = _ext.load()
+        self.ext = ext
+        layout = moe_slab_layout(cfg, world_size, ext.HEAP_HEADER_BYTES)
+        self.ws = SymmetricWorkspace(
+            layout, rank=rank, world_size=world_size, group=group, device=self.device, wait_limit_ms=wait_limit_ms
+        )
+        shape3 = (self.num_local_experts, self.max_recv, cfg.hidden_dim)
+        self.expert_x = self.ws.view("expert_x", shape3, cfg.in_dtype)
+        self.expert_y = self.ws.view("expert_y", shape3, cfg.out_dtype)
+        self.expert_meta = self.ws.view("expert_meta", (self.num_local_experts, self.max_recv, META_DIM), torch.int32)
+        n_max = max(cfg.max_num_tokens * cfg.experts_per_token, 1)
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self._blk_hist = torch.zeros(sms * cfg.num_experts, **i32)
+        self._local_rank = torch.zeros(n_max, **i32)
+        self._route = torch.full((n_max, 2), -1, **i32)
+        self.expert_num_tokens = torch.zeros(self.num_local_experts, **i32)
+        self._num_tokens = 0
+
+    # -- dispatch ----------------------------------------------------------------------
+    def dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        cfg = self.cfg
+        if dp_x.shape[0] > cfg.max_num_tokens:
+            raise ValueError(f"{dp_x.shape[0]} tokens exceed max_num_tokens={cfg.max_num_tokens}")
+        if dp_x.shape[1] != cfg.hidden_dim or indices.shape[1] != cfg.experts_per_token:
+            raise ValueError("dp_x / indices do not match the configuration")
+        if dp_x.dtype != cfg.in_dtype:
+            raise ValueError(f"dp_x is {dp_x.dtype}, configuration says {cfg.in_dtype}")
+        self.ws.check()
+        x = dp_x.contiguous()
+        idx = indices.to(torch.int32).contiguous()
+        self._num_tokens = x.shape[0]
+        self.ext.moe_dispatch(
+            self.ws.heap,
+            x,
+            idx,
+            cfg.num_experts,
+            self.max_recv,
+            self.ws.offset("counts"),
+            self.ws.offset("expert_x"),
+            self.ws.offset("expert_meta"),
+            self._blk_hist,
+            self._local_rank,
+            self._route,
+            self.expert_num_tokens,
+            self.ws.next_epoch("moe_dispatch"),
+            self.ws.wait_limit_ns,
+        )
+        return self.expert_num_tokens, self.expert_x, self.expert_meta
+
+    # -- expert op of the task ---------------------------------------------------------
+    def expert_scale(self, scale: float) -> torch.Tensor:
+        """``expert_y = expert_x * scale`` on the rows dispatch delivered
+        (all2all/reference.py:262 with ``scale = 1 + rank``)."""
+        self.ext.moe_expert_scale(self.expert_x, self.expert_y, self.expert_num_tokens, float(scale))
+        return self.expert_y
+
+    # -- combine -----------------------------------------------------------------------
+    def combine(
+        self,
+        out_tokens: torch.Tensor,
+        weights: torch.Tensor,
+        expert_meta: torch.Tensor,
+        expert_y: torch.Tensor,
+        expert_num_tokens: torch.Tensor,
+        num_tokens: Optional[int] = None,
+        accumulate: bool = False,
+    ) -> torch.Tensor:
+        """Weighted top-k sum of the expert outputs back into token order.
+
+        ``expert_meta`` / ``expert_num_tokens`` are accepted for interface parity; routing
+        comes from the table recorded by the preceding ``dispatch``.  ``expert_y`` may be
+        any tensor of the dispatch layout: if it is not this layer's symmetric buffer its
+        valid rows are first copied there so that peers can read them.  Rows
+        ``[0, num_tokens)`` of ``out_tokens`` are overwritten (``accumulate=True`` adds
+        instead, which equals the reference's ``+=`` onto a caller-provided buffer).
+        """
+        n = self._num_tokens if num_tokens is None else int(num_tokens)
+        if n != self._num_tokens:
+            raise ValueError("num_tokens differs from the preceding dispatch")
+        if expert_y.data_ptr() != self.expert_y.data_ptr():
+            if expert_y.shape != self.expert_y.shape or expert_y.dtype != self.expert_y.dtype:
+                raise ValueError("expert_y does not have the dispatch layout / out_dtype")
+            self.ext.moe_expert_scale(expert_y.contiguous(), self.expert_y, self.expert_num_tokens, 1.0)
+        target = out_tokens
+        if accumulate or not out_tokens.is_contiguous() or out_tokens.dtype != self.cfg.out_dtype:
+            target = torch.empty((max(n, 1), self.cfg.hidden_dim), dtype=self.cfg.out_dtype, device=out_tokens.device)
+        self.ext.moe_combine(
+            self.ws.heap,
+            target,
+            weights.to(torch.float32).contiguous(),
+            self._route,
+            n,
+            self.max_recv,
+            self.ws.offset("expert_y"),
+            self.ws.next_epoch("moe_combine"),
+            self.ws.wait_limit_ns,
+        )
+        if target is not out_tokens:
+            if accumulate:
+                out_tokens[:n] += target[:n].to(out_tokens.dtype)
+            else:
+                out_tokens[:n] = target[:n].to(out_tokens.dtype)
+        return out_tokens
+
+    def check(self, sync: bool = True) -> None:
+        self.ws.check(sync)
+
+    def close(self) -> None:
+        self.ws.close()
+
+
+# --------------------------------------------------------------------------------------
+# entry point
+# --------------------------------------------------------------------------------------
+
+_LAYERS: Dict[tuple, MoEAllToAll] = {}
+
+
+def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None) -> MoEAllToAll:
+    """Workspace creation is collective and costs milliseconds, so layers are cached per
+    configuration; the reference rebuilds its helper object on every call
+    (all2all/hipv8.py:379) because it owns no persistent state."""
+    key = (
+        cfg.num_experts,
+        cfg.experts_per_token,
+        cfg.hidden_dim,
+        cfg.max_num_tokens,
+        cfg.in_dtype,
+        cfg.out_dtype,
+        rank,
+        world_size,
+        id(group),
+        torch.cuda.current_device(),
+    )
+    layer = _LAYERS.get(key)
+    if layer is None:
+        layer = MoEAllToAll(cfg, rank, world_size, group)
+        _LAYERS[key] = layer
+    return layer
+
+
+def release_layers() -> None:
+    """Free every cached workspace (collective: all ranks must call it while idle)."""
+    for layer in _LAYERS.values():
+        layer.close()
+    _LAYERS.clear()
+
+
+def custom_kernel(data: MoEInput, backend: str = "auto") -> torch.Tensor:
+    """Dispatch -> ``* (1 + rank)`` -> combine; returns ``y[num_tokens, hidden]`` in
+    ``cfg.out_dtype`` on the rank's device (all2all/reference.py:256-272)."""
+    cfg, rank_data, rank, world_size = data
+    x = rank_data.x
+    if backend == "torch" or (backend == "auto" and not x.is_cuda):
+        ata = TorchAllToAll(cfg, rank, world_size)
+        n_tok, ex, em = ata.dispatch(x, rank_data.indices)
+        ey = ex.to(cfg.out_dtype) * (1 + rank)
+        y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=x.device)
+        ata.combine(y, rank_data.weights, em, ey, n_tok)
+        return y[: rank_data.num_tokens]
+    with torch.cuda.device(x.device):
+        layer = get_layer(cfg, rank, world_size)
+        n_tok, ex, em = layer.dispatch(x, rank_data.indices)
+        ey = layer.expert_scale(1 + rank)
+        y = torch.empty(rank_data.num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=x.device)
+        layer.combine(y, rank_data.weights, em, ey, n_tok, rank_data.num_tokens)
+    return y

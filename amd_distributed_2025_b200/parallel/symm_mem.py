@@ -1,0 +1,156 @@
+"""Symmetric workspaces: peer-mapped device memory plus the host side of its protocol.
+
+The reference has no such layer: ranks exchange data only through
+``torch.distributed`` collectives on ordinary tensors (all2all/hipv8.py:281-359,
+gemm-rs/reference.py:59).  Here a ``SymmetricWorkspace`` is one slab per rank with the
+same layout everywhere.  Creation is collective: every rank allocates, the CUDA IPC
+handles travel once through the existing process group (``all_gather_object``), every
+rank maps the peers' slabs, and a host barrier closes the set-up.  Afterwards kernels
+reach "offset X on rank r" with plain loads/stores over NVLink and synchronise through
+epoch-numbered flags in the slab header; the process group is not used again.
+
+``SlabLayout`` is the pure-Python bump allocator that assigns the offsets; because it is
+deterministic, all ranks derive identical layouts without communicating.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..utils.status import StatusError, describe_status
+
+DEFAULT_WAIT_LIMIT_MS = float(os.environ.get("B200_WAIT_LIMIT_MS", "10000"))
+
+
+def _align_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+class SlabLayout:
+    """Deterministic bump allocator over one slab; offsets are bytes from the slab base."""
+
+    def __init__(self, header_bytes: int, align: int = 1024):
+        self.align = align
+        self.cursor = _align_up(header_bytes, align)
+        self.regions: Dict[str, Tuple[int, int]] = {}
+
+    def add(self, name: str, nbytes: int, align: Optional[int] = None) -> int:
+        if name in self.regions:
+            raise KeyError(f"region {name!r} already allocated")
+        a = align or self.align
+        off = _align_up(self.cursor, a)
+        self.regions[name] = (off, int(nbytes))
+        self.cursor = off + int(nbytes)
+        return off
+
+    def offset(self, name: str) -> int:
+        return self.regions[name][0]
+
+    def size(self, name: str) -> int:
+        return self.regions[name][1]
+
+    @property
+    def total_bytes(self) -> int:
+        return _align_up(self.cursor, self.align)
+
+    def overlaps(self) -> bool:
+        spans = sorted(self.regions.values())
+        return any(a_off + a_len > b_off for (a_off, a_len), (b_off, _) in zip(spans, spans[1:]))
+
+
+class EpochCounter:
+    """Call numbers per protocol.  Flags carry the epoch of the call that set them, so
+    they never need resetting; all ranks must issue the same sequence of calls."""
+
+    def __init__(self):
+        self._epochs: Dict[str, int] = {}
+
+    def next(self, name: str) -> int:
+        v = self._epochs.get(name, 0) + 1
+        self._epochs[name] = v
+        return v
+
+    def current(self, name: str) -> int:
+        return self._epochs.get(name, 0)
+
+
+class SymmetricWorkspace:
+    """A peer-mapped slab with its layout, epochs and status word."""
+
+    def __init__(
+        self,
+        layout: SlabLayout,
+        *,
+        rank: Optional[int] = None,
+        world_size: Optional[int] = None,
+        group=None,
+        device: Optional[torch.device] = None,
+        wait_limit_ms: Optional[float] = None,
+    ):
+        from ..ops import _ext
+
+        self.ext = _ext.load()
+        self.group = group
+        initialized = dist.is_available() and dist.is_initialized()
+        self.world_size = world_size if world_size is not None else (dist.get_world_size(group) if initialized else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if initialized else 0)
+        if self.world_size > self.ext.MAX_WORLD_SIZE:
+            raise ValueError(f"world_size {self.world_size} exceeds the supported {self.ext.MAX_WORLD_SIZE}")
+        if self.world_size > 1 and not initialized:
+            raise RuntimeError("a process group is required to exchange memory handles")
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device)
+        self.layout = layout
+        self.epochs = EpochCounter()
+        self.wait_limit_ns = int((wait_limit_ms if wait_limit_ms is not None else DEFAULT_WAIT_LIMIT_MS) * 1e6)
+        dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.heap = self.ext.SymmHeap(self.rank, self.world_size, layout.total_bytes, dev_index)
+        if self.world_size > 1:
+            handles: List[Optional[bytes]] = [None] * self.world_size
+            dist.all_gather_object(handles, self.heap.ipc_handle(), group=group)
+            self.heap.open_peers(handles)
+            dist.barrier(group=group)
+        self._closed = False
+
+    # -- memory ------------------------------------------------------------------------
+    def view(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Tensor view of a region of the *local* slab (no copy; lifetime = workspace)."""
+        off, size = self.layout.regions[name]
+        need = int(torch.tensor([], dtype=dtype).element_size())
+        for s in shape:
+            need *= int(s)
+        if need > size:
+            raise ValueError(f"view of {need} bytes exceeds region {name!r} of {size} bytes")
+        return self.heap.view(off, list(shape), dtype)
+
+    def offset(self, name: str) -> int:
+        return self.layout.offset(name)
+
+    # -- protocol ----------------------------------------------------------------------
+    def next_epoch(self, name: str) -> int:
+        return self.epochs.next(name)
+
+    def barrier(self) -> None:
+        """Device-side barrier over all ranks on the current stream."""
+        self.heap.barrier(self.next_epoch("barrier"), self.wait_limit_ns)
+
+    def status(self, sync: bool = False) -> dict:
+        return self.heap.status_sync() if sync else self.heap.status()
+
+    def check(self, sync: bool = False) -> None:
+        """Raise ``StatusError`` if a kernel recorded a failure (expired wait, bad index)."""
+        st = self.status(sync)
+        if st["code"] != 0:
+            raise StatusError(describe_status(st, self.rank), st)
+
+    def reset_status(self) -> None:
+        self.heap.reset_status()
+
+    def close(self) -> None:
+        if not self._closed:
+            self._closed = True
+            self.heap.close()

@@ -1,0 +1,155 @@
+"""Single-GPU tests: every kernel at world_size 1 against plain PyTorch fp32/fp64 math."""
+import pytest
+import torch
+
+from amd_distributed_2025_b200 import contract, oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    from amd_distributed_2025_b200.ops import _ext
+
+    return _ext.load()
+
+
+def test_extension_is_loaded_from_tree():
+    mod = _ext()
+    assert mod.__file__.endswith("_C/b200_ext.so")
+
+
+def test_bounded_wait_times_out_and_context_survives():
+    from amd_distributed_2025_b200.parallel.symm_mem import SlabLayout, SymmetricWorkspace
+    from amd_distributed_2025_b200.utils.status import StatusError
+
+    ext = _ext()
+    ws = SymmetricWorkspace(SlabLayout(ext.HEAP_HEADER_BYTES), rank=0, world_size=1, wait_limit_ms=5)
+    ws.check(sync=True)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    ws.heap.wait_selftest(3, 12345, 5_000_000)  # a flag nothing sets, 5 ms limit
+    stop.record()
+    torch.cuda.synchronize()
+    assert 4.0 < start.elapsed_time(stop) < 500.0
+    with pytest.raises(StatusError) as err:
+        ws.check(sync=True)
+    assert err.value.code == "timeout" and err.value.phase == "selftest" and err.value.status["peer"] == 3
+    assert ws.status()["code"] == 1  # host mirror, no synchronisation needed
+    ws.reset_status()
+    ws.check(sync=True)
+    # the context is still usable
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+    ws.barrier()
+    torch.cuda.synchronize()
+    ws.check(sync=True)
+    ws.close()
+
+
+@pytest.mark.parametrize(
+    "E,k,H,T,dtype,fixed",
+    [
+        (8, 2, 6144, 4, torch.float16, None),
+        (64, 6, 2048, 8, torch.float16, None),
+        (128, 4, 2880, 32, torch.float16, None),
+        (256, 8, 7168, 128, torch.bfloat16, 128),
+        (16, 2, 256, 32, torch.float32, 32),
+        (64, 6, 1024, 1024, torch.bfloat16, 1024),
+        (8, 2, 250, 5, torch.float16, 5),  # row size not a multiple of 16 bytes: scalar paths
+    ],
+)
+def test_moe_world1_matches_oracle(E, k, H, T, dtype, fixed):
+    from amd_distributed_2025_b200.models import moe_all2all
+
+    cfg, data, rank, ws = contract.make_moe_inputs(E, k, H, T, 7, 0, 1, device="cuda", dtype=dtype,
+                                                   fixed_num_tokens=fixed, routing="zipf" if T >= 1024 else "uniform",
+                                                   weights="softmax")
+    layer = moe_all2all.get_layer(cfg, 0, 1)
+    got = layer.dispatch(data.x, data.indices)
+    torch.cuda.synchronize()
+    layer.check()
+    ok, msg = oracle.compare_dispatch_layout(got, oracle.moe_dispatch_oracle(cfg, [data], 0))
+    assert ok, msg
+    for _ in range(3):  # repeated calls exercise the epoch-numbered flags
+        y = moe_all2all.custom_kernel((cfg, data, 0, 1))
+    torch.cuda.synchronize()
+    layer.check()
+    want = oracle.moe_expected_output(cfg, data, 1)
+    ok, msg = oracle.check_moe_output(y, want)
+    assert ok, msg
+    assert oracle.relative_error(y, oracle.moe_expected_output(cfg, data, 1, acc_dtype=torch.float64)) < 5e-3
+
+
+def test_moe_combine_accepts_foreign_expert_y():
+    from amd_distributed_2025_b200.models import moe_all2all
+
+    cfg, data, _, _ = contract.make_moe_inputs(32, 4, 512, 64, 3, 0, 1, device="cuda", fixed_num_tokens=64)
+    layer = moe_all2all.get_layer(cfg, 0, 1)
+    n_tok, ex, em = layer.dispatch(data.x, data.indices)
+    ey = ex.clone() * 3  # an ordinary tensor, not the symmetric buffer
+    y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device="cuda")
+    layer.combine(y, data.weights, em, ey, n_tok, data.num_tokens)
+    torch.cuda.synchronize()
+    want = (data.x.float() * 3 * data.weights.sum(1, keepdim=True)).to(cfg.out_dtype)
+    assert torch.allclose(y[: data.num_tokens].float(), want.float(), rtol=1e-2, atol=5e-3)
+
+
+def test_moe_bad_expert_id_is_reported_not_faulted():
+    from amd_distributed_2025_b200.models import moe_all2all
+    from amd_distributed_2025_b200.utils.status import StatusError
+
+    cfg, data, _, _ = contract.make_moe_inputs(16, 2, 128, 8, 3, 0, 1, device="cuda", fixed_num_tokens=8)
+    layer = moe_all2all.MoEAllToAll(cfg, 0, 1)
+    bad = data.indices.clone()
+    bad[2, 1] = 99
+    layer.dispatch(data.x, bad)
+    torch.cuda.synchronize()
+    with pytest.raises(StatusError) as err:
+        layer.check()
+    assert err.value.code == "bad_index"
+    layer.ws.reset_status()
+    layer.close()
+
+
+@pytest.mark.parametrize(
+    "m,n,k,has_bias",
+    [
+        (128, 256, 64, False),      # one tile, one k-block
+        (128, 256, 512, True),
+        (256, 512, 1024, True),
+        (64, 2880, 360, True),      # ragged M, N and K (K/8 of the smallest task shape)
+        (2048, 5120, 1600, True),
+        (512, 4608, 4608, False),
+        (1024, 8192, 3584, True),
+    ],
+)
+def test_gemm_world1_matches_fp32_reference(m, n, k, has_bias):
+    from amd_distributed_2025_b200.models import gemm_rs
+
+    a, w, bias = contract.make_gemm_rs_inputs(0, 1, m, n, k, has_bias, 5, device="cuda")
+    out = gemm_rs.custom_kernel((a, w, bias))
+    torch.cuda.synchronize()
+    gemm_rs.get_op(m, n).check()
+    truth = a.float() @ w.float().T
+    if has_bias:
+        truth = truth + bias.float()
+    ok, msg = oracle.check_gemm_rs_output(out, truth.to(torch.bfloat16))
+    assert ok, msg
+    assert oracle.relative_error(out, truth) < 5e-3
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+def test_gemm_tile_widths(block_n):
+    from amd_distributed_2025_b200.models import gemm_rs
+
+    m, n, k = 384, 1024, 832
+    a, w, bias = contract.make_gemm_rs_inputs(0, 1, m, n, k, True, 9, device="cuda")
+    op = gemm_rs.get_op(m, n)
+    op.block_n = block_n
+    try:
+        out = op(a, w, bias)
+        torch.cuda.synchronize()
+        op.check()
+    finally:
+        op.block_n = 0
+    truth = a.float() @ w.float().T + bias.float()
+    assert oracle.relative_error(out, truth) < 5e-3
