@@ -175,8 +175,8 @@ void moe_combine(SymmHeap& heap, at::Tensor out, const at::Tensor& weights, cons
 // ------------------------------------------------------------------------- GEMM-RS ----
 
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
-             at::Tensor out, double bias_scale, int64_t off_stage, int64_t off_counters, int64_t epoch,
-             int64_t timeout_ns, int64_t max_ctas, int64_t block_n) {
+             at::Tensor out, double bias_scale, bool bias_at_source, int64_t off_stage, int64_t off_counters, int64_t epoch,
+             int64_t timeout_ns, int64_t max_ctas, int64_t block_n, int64_t cta_pair) {
   TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
               "input and weight must be bf16 CUDA tensors");
@@ -205,6 +205,7 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.world_size = ws;
   g.rank = heap.rank();
   g.bias_scale = (float)bias_scale;
+  g.bias_at_source = bias_at_source ? 1 : 0;
   fill_peer_bases(heap, g.peer_base);
   g.off_stage = (uint64_t)off_stage;
   g.off_counters = (uint64_t)off_counters;
@@ -214,6 +215,7 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.sync_counters = heap.sync_counters() + 8;
   g.max_ctas = (int)max_ctas;
   g.block_n = (int)block_n;
+  g.cta_pair = (int)cta_pair;
   cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
 }
 

@@ -32,7 +32,9 @@ struct GemmRsArgs {
   const void* bias;  // [N] bf16 or nullptr
   void* out;         // [M / world_size, N] bf16
   int M, N, K, world_size, rank;
-  float bias_scale;  // world_size to match the reference checker, 1 to add the bias once
+  float bias_scale;  // multiplier of the bias when it is added once by the owning rank
+  int bias_at_source;  // 1: every rank adds the bias to its own bf16 partial before the reduction, as the
+                       // reference does (gemm-rs/reference.py:54-59), so the result holds world_size * bias
   uint64_t peer_base[kMaxWorldSize];
   uint64_t off_stage;     // staging buffer of the current parity: bf16 [world][M/ws][N]
   uint64_t off_counters;  // arrival counters of the current parity: uint32 [m_tiles][n_tiles]
@@ -42,6 +44,7 @@ struct GemmRsArgs {
   uint32_t* sync_counters;
   int max_ctas;  // 0 = one per SM
   int block_n;   // 0 = choose from the shape; else 64, 128 or 256
+  int cta_pair;  // -1 = choose from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
 };
 
 // Bytes of ONE parity of the staging buffer / the counters for a problem.

@@ -1,5 +1,9 @@
 // Fused GEMM + reduce-scatter kernel for sm_100a (see gemm_rs.h for the capability).
 //
+// Two schedules share the code: one CTA per 128 x BN tile, or a CTA pair (cluster of two,
+// tcgen05 cta_group::2) per 256 x BN tile, where each CTA loads half of the W tile and the
+// leader's single MMA instruction feeds both tensor-memory halves.  No load is multicast.
+//
 // Warp roles inside one persistent CTA (192 threads, one CTA per SM):
 //   warp 0        TMA producer: fills a ring of shared-memory stages with A and W tiles
 //   warp 1        MMA issuer: one lane issues tcgen05.mma, accumulating in tensor memory;
@@ -33,11 +37,16 @@ constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in maximum per CTA
 
-template <int BN>
+// BN: tile width.  CTAS: 1 = one CTA per 128 x BN tile; 2 = a CTA pair (cluster of two) owns a
+// 256 x BN tile: each CTA loads its own 128 rows of A and HALF of the W tile, the leader
+// issues one M=256 MMA for both, and each CTA's tensor memory receives its 128 rows.
+template <int BN, int CTAS>
 struct Cfg {
   static constexpr int kABytes = BM * BK * 2;           // 16 KiB
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBRows = BN / CTAS;              // W rows this CTA loads per stage
+  static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTxBytes = CTAS * kStageBytes;   // bytes counted on the (leader's) full barrier
   static constexpr int kEpiCols = BN < 128 ? BN : 128;  // columns transposed at a time
   static constexpr int kSlabBytes = 32 * kEpiCols * 2;  // per epilogue warp
   static constexpr int kEpiBytes = kEpilogueWarps * kSlabBytes;
@@ -46,8 +55,10 @@ struct Cfg {
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two >= 32
+  static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
   static_assert(kStages >= 3, "pipeline too shallow");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
+  static_assert(kBRows % 8 == 0 && kBRows <= 256, "W box rows");
 };
 
 struct KernelParams {
@@ -55,9 +66,11 @@ struct KernelParams {
   __nv_bfloat16* out;
   int M, N, K, world_size, rank;
   int rows_per_rank;
-  int m_tiles, n_tiles, num_kb;
-  int m_start;  // first m-tile of the rotated order (the one after this rank's rows)
+  int m_tiles, n_tiles, num_kb;  // m_tiles counts 128-row blocks
+  int m_groups;  // row groups of 128 * CTAS rows: the scheduling unit along M
+  int m_start;   // first row group of the rotated order (the one after this rank's rows)
   float bias_scale;
+  int bias_at_source;  // 1: every rank adds the bias to its rounded partial (the reference's order of operations)
   uint64_t peer_base[kMaxWorldSize];
   uint64_t off_stage, off_counters;
   uint64_t epoch, timeout_ns;
@@ -99,20 +112,81 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ void tile_coords(const KernelParams& p, int t, int& mb, int& nb) {
+// Work item t of this CTA (pair): row group (rotated so the rank's own rows come last) and
+// column tile; `mb` is the 128-row block this CTA computes.
+template <int CTAS>
+__device__ __forceinline__ void tile_coords(const KernelParams& p, int t, uint32_t cta_rank, int& mb, int& nb) {
   const int j = t / p.n_tiles;
   nb = t - j * p.n_tiles;
-  mb = p.m_start + j;
-  if (mb >= p.m_tiles) mb -= p.m_tiles;
+  int mg = p.m_start + j;
+  if (mg >= p.m_groups) mg -= p.m_groups;
+  mb = mg * CTAS + (int)cta_rank;
+}
+
+// True when every row of m-tile `mb` belongs to this rank (and lies inside M).
+__device__ __forceinline__ bool tile_owned(const KernelParams& p, int mb) {
+  const int lo = mb * BM;
+  const int row_lo = p.rank * p.rows_per_rank;
+  return lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
+}
+
+// Sum of the world_size bf16 partial vectors of out[rl, n..n+8) in rank order, in fp32,
+// plus the bias, rounded once.  `own` (if given) is this rank's partial, taken from
+// registers instead of the staging buffer.
+__device__ __forceinline__ uint4 reduce_partials(const KernelParams& p, const __nv_bfloat16* stage, int rl, int n,
+                                                 const uint4* own) {
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  const size_t R = (size_t)p.rows_per_rank;
+  for (int s0 = 0; s0 < p.world_size; s0 += 8) {
+    uint4 vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int s = s0 + u;
+      if (s < p.world_size) {
+        if (own != nullptr && s == p.rank) vals[u] = *own;
+        else vals[u] = __ldcg(reinterpret_cast<const uint4*>(stage + ((size_t)s * R + rl) * p.N + n));
+      } else {
+        vals[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  }
+  if (p.bias != nullptr && !p.bias_at_source) {
+    const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      acc[2 * e] = fmaf(f.x, p.bias_scale, acc[2 * e]);
+      acc[2 * e + 1] = fmaf(f.y, p.bias_scale, acc[2 * e + 1]);
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  return o;
 }
 
 }  // namespace
 
-template <int BN>
+template <int BN, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                const KernelParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CTAS>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_flag;
   __shared__ uint32_t tmem_base_shared;
@@ -121,9 +195,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  const uint32_t cta_rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
 
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t smem_a0 = smem_base;                              // stage s: + s * kStageBytes
   const uint32_t smem_epi = smem_base + C::kStages * C::kStageBytes;
   const uint32_t bar_base = smem_epi + C::kEpiBytes;
@@ -135,12 +210,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (tid == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(full_bar(s), 1);   // one arrive (with the byte count) per phase, by the leader's producer
+      ptx::mbar_init(empty_bar(s), 1);  // one commit per phase, by the MMA issuer (to both CTAs of a pair)
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(tfull_bar(s), 1);
-      ptx::mbar_init(tempty_bar(s), kEpilogueWarps);
+      ptx::mbar_init(tempty_bar(s), kEpilogueWarps * CTAS);  // every epilogue warp of the pair
     }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -150,43 +225,59 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     ptx::prefetch_tensormap(&tma_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_shared), C::kTmemCols);
-    ptx::tmem_relinquish();
+    if (CTAS == 2) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_shared), C::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&tmem_base_shared), C::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
+  if (CTAS == 2) ptx::cluster_sync_all();  // the peer's barriers exist before anything signals them
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_shared;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
-  const int G = gridDim.x;
+  const int total_tiles = p.m_groups * p.n_tiles;
+  const int G = gridDim.x;              // CTAs
+  const int GG = G / CTAS;              // CTAs or CTA pairs: the schedulers
+  const int gidx = (int)blockIdx.x / CTAS;
   const uint64_t limit = p.timeout_ns;
 
   if (warp == 0) {
     // ================================ TMA producer =====================================
+    // Runs in every CTA: its own 128 rows of A and its share of the W tile.
     if (lane == 0) {
       PipeState ps;
-      for (int t = blockIdx.x; t < total_tiles && !abort_flag; t += G) {
+      for (int t = gidx; t < total_tiles && !abort_flag; t += GG) {
         int mb, nb;
-        tile_coords(p, t, mb, nb);
+        tile_coords<CTAS>(p, t, cta_rank, mb, nb);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, &abort_flag, limit, p.status, 100 + (int)ps.stage)) break;
           const uint32_t sa = smem_a0 + ps.stage * C::kStageBytes;
           const uint32_t sb = sa + C::kABytes;
-          ptx::mbar_arrive_expect_tx(full_bar(ps.stage), C::kStageBytes);
-          ptx::tma_load_2d(sa, &tma_a, full_bar(ps.stage), kb * BK, mb * BM);
-          ptx::tma_load_2d(sb, &tma_b, full_bar(ps.stage), kb * BK, nb * BN);
+          if (CTAS == 2) {
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(ps.stage), C::kTxBytes);
+            ptx::tma_load_2d_pair(sa, &tma_a, full_bar(ps.stage), kb * BK, mb * BM);
+            ptx::tma_load_2d_pair(sb, &tma_b, full_bar(ps.stage), kb * BK, nb * BN + (int)cta_rank * C::kBRows);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar(ps.stage), C::kTxBytes);
+            ptx::tma_load_2d(sa, &tma_a, full_bar(ps.stage), kb * BK, mb * BM);
+            ptx::tma_load_2d(sb, &tma_b, full_bar(ps.stage), kb * BK, nb * BN);
+          }
           ps.advance(C::kStages);
         }
       }
     }
   } else if (warp == 1) {
     // ================================ MMA issuer =======================================
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_bf16_f32(BM, BN);
+    // One lane of the (leader) CTA; in a pair the same instruction drives both CTAs.
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = ptx::make_idesc_bf16_f32(BM * CTAS, BN);
       PipeState ps;
       uint32_t it = 0;
-      for (int t = blockIdx.x; t < total_tiles && !abort_flag; t += G, ++it) {
+      for (int t = gidx; t < total_tiles && !abort_flag; t += GG, ++it) {
         const uint32_t acc = it & 1u;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, limit, p.status, 200 + (int)acc)) break;
@@ -206,13 +297,18 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j) {
             // advancing K by 16 bf16 = 32 bytes = 2 descriptor address units
-            ptx::umma_bf16(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            if (CTAS == 2) ptx::umma_bf16_pair(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            else ptx::umma_bf16(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
-          ptx::umma_commit(empty_bar(ps.stage));  // stage reusable once these MMAs have read it
+          // stage reusable (in both CTAs of a pair) once these MMAs have read it
+          if (CTAS == 2) ptx::umma_commit_pair(empty_bar(ps.stage), 3);
+          else ptx::umma_commit(empty_bar(ps.stage));
           ps.advance(C::kStages);
         }
         if (!ok) break;
-        ptx::umma_commit(tfull_bar(acc));  // accumulator complete
+        // accumulator complete: wake the epilogue warps (of both CTAs)
+        if (CTAS == 2) ptx::umma_commit_pair(tfull_bar(acc), 3);
+        else ptx::umma_commit(tfull_bar(acc));
       }
     }
   } else {
@@ -223,17 +319,25 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     constexpr int kRowsPerStore = 32 / kChunksPerRow;    // slab rows covered by one warp store
     constexpr int kRowPitch = C::kEpiCols * 2;
     const bool direct = (p.world_size == 1);
-    const uint64_t my_counter_off = p.off_counters;
+    const int R = p.rows_per_rank;
+    const int row_lo = p.rank * R;
+    uint32_t* my_counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
+    const __nv_bfloat16* my_stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
     uint32_t it = 0;
-    for (int t = blockIdx.x; t < total_tiles && !abort_flag; t += G, ++it) {
+    for (int t = gidx; t < total_tiles && !abort_flag; t += GG, ++it) {
       int mb, nb;
-      tile_coords(p, t, mb, nb);
+      tile_coords<CTAS>(p, t, cta_rank, mb, nb);
       const uint32_t acc = it & 1u;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, limit, p.status, 400 + (int)acc)) break;
       ptx::tcgen05_fence_after();
       const int m0 = mb * BM + q * 32;
       const int n0 = nb * BN;
+      // A tile whose rows all belong to this rank is finished here: the peers' partial rows
+      // are added in the store loop and the result goes straight to `out`.
+      const bool owned = !direct && tile_owned(p, mb);
+      const size_t ctr_index = ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps + q;
+      bool peers_ok = true;
 #pragma unroll 1
       for (int half = 0; half < BN / C::kEpiCols; ++half) {
         // ---- TMEM -> registers -> bf16 -> swizzled slab (row = lane) --------------------
@@ -243,13 +347,23 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * C::kEpiCols + c * 32;
           ptx::tmem_ld_32x32b_x32(taddr, v);
           ptx::tmem_ld_wait();
-          if (direct && p.bias != nullptr) {
+          if (p.bias != nullptr && (direct || p.bias_at_source)) {
             const int nbase = n0 + half * C::kEpiCols + c * 32;
+            if (p.bias_at_source) {
+              // reference order: round the product to bf16, add the bf16 bias, round again
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = nbase + j;
-              const float b = (n < p.N) ? __bfloat162float(p.bias[n]) * p.bias_scale : 0.f;
-              v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+              for (int j = 0; j < 32; ++j) {
+                const int n = nbase + j;
+                const float b = (n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+                v[j] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j]))) + b);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int n = nbase + j;
+                const float b = (n < p.N) ? __bfloat162float(p.bias[n]) * p.bias_scale : 0.f;
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+              }
             }
           }
 #pragma unroll
@@ -270,11 +384,28 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           // all TMEM reads of this accumulator are done: hand it back to the MMA warp
           ptx::tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if (CTAS == 2) ptx::mbar_arrive_cluster(tempty_bar(acc), 0);  // the leader's barrier
+            else ptx::mbar_arrive(tempty_bar(acc));
+          }
         }
         __syncwarp();
+        if (owned && half == 0) {
+          // Rows q*32..q*32+31 of this tile were stored by warp q of every peer; wait for
+          // their world_size - 1 arrivals on this warp's counter.
+          int ok = 1;
+          if (lane == 0) {
+            ok = wait_u32_ge(my_counters + ctr_index, (uint32_t)(p.world_size - 1), limit, p.status, PHASE_RS_PARTIALS,
+                             -1, (int)(mb * p.n_tiles + nb), true)
+                     ? 1
+                     : 0;
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          peers_ok = ok != 0;
+          if (!peers_ok) abort_flag = 1;
+        }
         // ---- slab -> global, whole row segments per store ------------------------------
-#pragma unroll
+#pragma unroll 2
         for (int s = 0; s < kChunksPerRow; ++s) {
           const int rr = s * kRowsPerStore + lane / kChunksPerRow;
           const int cc = lane % kChunksPerRow;
@@ -289,29 +420,36 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (m < p.M && n < p.N) {
             if (direct) {
               *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = val;
+            } else if (owned) {
+              if (peers_ok) {
+                const int rl = m - row_lo;
+                *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) =
+                    reduce_partials(p, my_stage, rl, n, &val);
+              }
             } else {
-              const int owner = m / p.rows_per_rank;
-              const int rl = m - owner * p.rows_per_rank;
+              const int owner = m / R;
+              const int rl = m - owner * R;
               __nv_bfloat16* dst = peer_ptr<__nv_bfloat16>(p.peer_base[owner], p.off_stage) +
-                                   ((size_t)p.rank * p.rows_per_rank + rl) * p.N + n;
+                                   ((size_t)p.rank * R + rl) * p.N + n;
               *reinterpret_cast<uint4*>(dst) = val;
             }
           }
         }
         __syncwarp();
       }
-      if (!direct) {
-        // Tell every owner with rows in this tile that this warp's part has been stored.
+      if (owned) {
+        if (lane == 0) my_counters[ctr_index] = 0;  // next used by the call after next
+      } else if (!direct) {
+        // Tell every owner with rows in this tile that warp q's 32 rows have been stored.
         __syncwarp();
         if (lane == 0) {
           __threadfence_system();
           const int m_lo = mb * BM;
           const int m_hi = min(p.M, m_lo + BM) - 1;
-          const int o_lo = m_lo / p.rows_per_rank;
-          const int o_hi = m_hi / p.rows_per_rank;
+          const int o_lo = m_lo / R;
+          const int o_hi = m_hi / R;
           for (int o = o_lo; o <= o_hi; ++o) {
-            uint32_t* ctr = peer_ptr<uint32_t>(p.peer_base[o], my_counter_off) + ((size_t)mb * p.n_tiles + nb);
-            red_release_sys_add(ctr, 1u);
+            red_release_sys_add(peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + ctr_index, 1u);
           }
         }
       }
@@ -326,91 +464,62 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
+  // A CTA of a pair must not retire while its partner may still signal its barriers or
+  // read its shared memory through the shared MMA.
+  if (CTAS == 2) ptx::cluster_sync_all();
   ptx::tcgen05_fence_after();
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    if (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
   if (p.world_size == 1 || abort_flag) return;
 
-  // ================================ reduction of this rank's rows ========================
-  // Blocks of the global tiling that contain rows owned by this rank; block j is reduced
-  // by CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles start first.
+  // ================================ reduction of shared tiles =============================
+  // Tiles that straddle an ownership boundary (always the case when a rank owns fewer than
+  // 128 rows) were staged by every rank, this one included.  Block j of them is reduced by
+  // CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles start first.
   const int R = p.rows_per_rank;
   const int row_lo = p.rank * R;
   const int mb_lo = row_lo / BM;
   const int mb_hi = (row_lo + R - 1) / BM;
-  const int blocks = (mb_hi - mb_lo + 1) * p.n_tiles;
-  const uint32_t want = (uint32_t)(p.world_size * kEpilogueWarps);
   uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
   const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
-  (void)smem_gen;
-  for (int j = (G - 1 - (int)blockIdx.x); j < blocks; j += G) {
-    const int mb = mb_lo + j / p.n_tiles;
-    const int nb = j % p.n_tiles;
-    uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb);
-    if (tid == 0) {
-      wait_ok_shared = wait_u32_ge(ctr, want, limit, p.status, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb, true);
-    }
-    __syncthreads();
-    const bool ok = wait_ok_shared != 0;
-    if (ok) {
-      const int r0 = max(mb * BM, row_lo);
-      const int r1 = min(min((mb + 1) * BM, row_lo + R), p.M);
-      const int c0 = nb * BN;
-      const int c1 = min(c0 + BN, p.N);
-      const int vec_per_row = (c1 - c0) >> 3;
-      const int items = (r1 - r0) * vec_per_row;
-      for (int i = tid; i < items; i += kThreads) {
-        const int r = r0 + i / vec_per_row;
-        const int n = c0 + ((i % vec_per_row) << 3);
-        const int rl = r - row_lo;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int s0 = 0; s0 < p.world_size; s0 += 8) {
-          uint4 vals[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int s = s0 + u;
-            if (s < p.world_size) {
-              vals[u] = __ldcg(reinterpret_cast<const uint4*>(stage + ((size_t)s * R + rl) * p.N + n));
-            } else {
-              vals[u] = make_uint4(0, 0, 0, 0);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(h[e]);
-              acc[2 * e] += f.x;
-              acc[2 * e + 1] += f.y;
-            }
-          }
+  int j = 0;
+  for (int mb = mb_lo; mb <= mb_hi; ++mb) {
+    if (tile_owned(p, mb)) continue;
+    for (int nb = 0; nb < p.n_tiles; ++nb, ++j) {
+      if (j % G != G - 1 - (int)blockIdx.x) continue;
+      uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps;
+      if (tid == 0) {
+        int ok = 1;
+        for (int w = 0; w < kEpilogueWarps && ok; ++w) {
+          ok = wait_u32_ge(ctr + w, (uint32_t)p.world_size, limit, p.status, PHASE_RS_PARTIALS, -1,
+                           mb * p.n_tiles + nb, true)
+                   ? 1
+                   : 0;
         }
-        if (p.bias != nullptr) {
-          const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            acc[2 * e] = fmaf(f.x, p.bias_scale, acc[2 * e]);
-            acc[2 * e + 1] = fmaf(f.y, p.bias_scale, acc[2 * e + 1]);
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]);
-        o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]);
-        o.w = pack_bf16x2(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) = o;
+        wait_ok_shared = ok;
       }
+      __syncthreads();
+      const bool ok = wait_ok_shared != 0;
+      if (ok) {
+        const int r0 = max(mb * BM, row_lo);
+        const int r1 = min(min((mb + 1) * BM, row_lo + R), p.M);
+        const int c0 = nb * BN;
+        const int c1 = min(c0 + BN, p.N);
+        const int vec_per_row = (c1 - c0) >> 3;
+        const int items = (r1 - r0) * vec_per_row;
+        for (int i = tid; i < items; i += kThreads) {
+          const int rl = r0 + i / vec_per_row - row_lo;
+          const int n = c0 + ((i % vec_per_row) << 3);
+          *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) = reduce_partials(p, stage, rl, n, nullptr);
+        }
+      }
+      __syncthreads();
+      if (tid < kEpilogueWarps) ctr[tid] = 0;  // this parity's counters are next used two calls from now
+      if (!ok) return;
     }
-    __syncthreads();
-    if (tid == 0) *ctr = 0;  // this parity's counter is next used two calls from now
-    if (!ok) break;
   }
 }
 
@@ -452,22 +561,35 @@ bool make_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS;
 }
 
-int pick_block_n(int M, int N, int sms) {
+// Tile shape from the problem size: CTA pairs with 256-row tiles once the problem fills the
+// machine, single CTAs with narrower tiles for small problems.
+void pick_config(int M, int N, int sms, int& bn, int& ctas) {
   const int m_tiles = (M + BM - 1) / BM;
-  // widest tile that still gives every SM a tile; narrow tiles only for small problems
-  for (int bn : {256, 128}) {
-    const int tiles = m_tiles * ((N + bn - 1) / bn);
-    if (tiles >= sms) return bn;
+  const int pairs = sms / 2;
+  for (int cand : {256, 128}) {
+    const int tiles = ((m_tiles + 1) / 2) * ((N + cand - 1) / cand);
+    if (tiles >= pairs) {
+      bn = cand;
+      ctas = 2;
+      return;
+    }
   }
-  return 64;
+  ctas = 1;
+  for (int cand : {128}) {
+    if (m_tiles * ((N + cand - 1) / cand) >= sms) {
+      bn = cand;
+      return;
+    }
+  }
+  bn = 64;
 }
 
-template <int BN>
+template <int BN, int CTAS>
 cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CTAS>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map(&map_a, a.a, (uint64_t)a.M, (uint64_t)a.K, BM)) return cudaErrorInvalidValue;
-  if (!make_tensor_map(&map_b, a.w, (uint64_t)a.N, (uint64_t)a.K, BN)) return cudaErrorInvalidValue;
+  if (!make_tensor_map(&map_b, a.w, (uint64_t)a.N, (uint64_t)a.K, C::kBRows)) return cudaErrorInvalidValue;
 
   KernelParams p;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
@@ -481,9 +603,12 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
   p.m_tiles = (a.M + BM - 1) / BM;
   p.n_tiles = (a.N + BN - 1) / BN;
   p.num_kb = (a.K + BK - 1) / BK;
-  // rotated order: start with the first tile wholly after this rank's rows
-  p.m_start = (int)((((int64_t)(a.rank + 1) * p.rows_per_rank + BM - 1) / BM) % p.m_tiles);
+  p.m_groups = (p.m_tiles + CTAS - 1) / CTAS;
+  // rotated order: start with the first row group wholly after this rank's rows
+  const int64_t group_rows = (int64_t)BM * CTAS;
+  p.m_start = (int)((((int64_t)(a.rank + 1) * p.rows_per_rank + group_rows - 1) / group_rows) % p.m_groups);
   p.bias_scale = a.bias_scale;
+  p.bias_at_source = a.bias_at_source;
   for (int r = 0; r < kMaxWorldSize; ++r) p.peer_base[r] = a.peer_base[r];
   p.off_stage = a.off_stage;
   p.off_counters = a.off_counters;
@@ -491,16 +616,36 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
 
-  {
-    cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (e != cudaSuccess) return e;
+  auto kernel = gemm_rs_kernel<BN, CTAS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+
+  const int total = p.m_groups * p.n_tiles;
+  int schedulers = std::min(total, sms / CTAS);
+  if (a.max_ctas > 0) schedulers = std::min(schedulers, std::max(a.max_ctas / CTAS, 1));
+  if (schedulers < 1) schedulers = 1;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(schedulers * CTAS));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (CTAS == 2 && a.max_ctas <= 0) {
+    // never launch more pairs than can be resident at once
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) == cudaSuccess && max_clusters > 0 &&
+        max_clusters < schedulers) {
+      cfg.gridDim = dim3((unsigned)(max_clusters * CTAS));
+    }
   }
-  const int total = p.m_tiles * p.n_tiles;
-  int grid = std::min(total, sms);
-  if (a.max_ctas > 0) grid = std::min(grid, a.max_ctas);
-  if (grid < 1) grid = 1;
-  gemm_rs_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
-  return cudaGetLastError();
+  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
 }
 
 }  // namespace
@@ -514,7 +659,7 @@ uint64_t gemm_rs_counter_bytes(int M, int N, int world_size) {
   (void)world_size;
   const uint64_t m_tiles = (M + BM - 1) / BM;
   const uint64_t n_tiles = (N + 63) / 64;
-  return (m_tiles * n_tiles * 4 + 255) / 256 * 256;
+  return (m_tiles * n_tiles * kEpilogueWarps * 4 + 255) / 256 * 256;
 }
 
 cudaError_t launch_gemm_rs(const GemmRsArgs& a, cudaStream_t stream) {
@@ -523,11 +668,22 @@ cudaError_t launch_gemm_rs(const GemmRsArgs& a, cudaStream_t stream) {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int bn = a.block_n > 0 ? a.block_n : pick_block_n(a.M, a.N, sms);
+  int bn = 0, ctas = 0;
+  pick_config(a.M, a.N, sms, bn, ctas);
+  if (a.block_n > 0) bn = a.block_n;
+  if (a.cta_pair >= 0) ctas = a.cta_pair ? 2 : 1;
+  if (ctas == 2 && bn == 64) ctas = 1;
+  if (ctas == 2) {
+    switch (bn) {
+      case 256: return launch_typed<256, 2>(a, sms, stream);
+      case 128: return launch_typed<128, 2>(a, sms, stream);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (bn) {
-    case 256: return launch_typed<256>(a, sms, stream);
-    case 128: return launch_typed<128>(a, sms, stream);
-    case 64: return launch_typed<64>(a, sms, stream);
+    case 256: return launch_typed<256, 1>(a, sms, stream);
+    case 128: return launch_typed<128, 1>(a, sms, stream);
+    case 64: return launch_typed<64, 1>(a, sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

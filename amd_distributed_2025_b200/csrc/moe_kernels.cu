@@ -52,15 +52,15 @@ __device__ __forceinline__ void warp_copy_row(const uint8_t* __restrict__ src, u
     const int4* s = reinterpret_cast<const int4*>(src);
     int4* d = reinterpret_cast<int4*>(dst);
     const int nv = bytes >> 4;
-    for (int v = lane; v < nv; v += 32 * 4) {
-      int4 r[4];
+    for (int v = lane; v < nv; v += 32 * 8) {
+      int4 r[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int idx = v + u * 32;
         if (idx < nv) r[u] = __ldg(s + idx);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int idx = v + u * 32;
         if (idx < nv) d[idx] = r[u];
       }
@@ -255,14 +255,24 @@ template <typename TIn, typename TOut>
 __global__ void moe_expert_scale_kernel(const TIn* __restrict__ x, TOut* __restrict__ y,
                                         const int32_t* __restrict__ num_tokens, int num_local_experts,
                                         int max_recv, int hidden, float scale) {
-  extern __shared__ int32_t prefix[];  // [E_local + 1]
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int e = 0; e < num_local_experts; ++e) {
-      prefix[e] = acc;
-      acc += min(max(num_tokens[e], 0), max_recv);
+  extern __shared__ int32_t prefix[];  // [E_local + 1] exclusive prefix of the valid row counts
+  // Block-wide exclusive scan, 32 experts per step of warp 0.
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    for (int base = 0; base < num_local_experts; base += 32) {
+      const int e = base + lane;
+      const int v = e < num_local_experts ? min(max(num_tokens[e], 0), max_recv) : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (e < num_local_experts) prefix[e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    prefix[num_local_experts] = acc;
+    if (lane == 0) prefix[num_local_experts] = carry;
   }
   __syncthreads();
   const int total_rows = prefix[num_local_experts];
@@ -280,7 +290,32 @@ __global__ void moe_expert_scale_kernel(const TIn* __restrict__ x, TOut* __restr
     // The reference rounds the scale to out_dtype before multiplying in out_dtype
     // (tensor * python int); (1 + rank) is exactly representable, so one rounding of
     // the fp32 product gives the same value.
-    for (int h = lane; h < hidden; h += 32) dst[h] = from_f32<TOut>(to_f32(src[h]) * scale);
+    constexpr int kVec = 16 / sizeof(TIn);
+    if (sizeof(TIn) == sizeof(TOut) && hidden % kVec == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      const int nv = hidden / kVec;
+      const int4* s4 = reinterpret_cast<const int4*>(src);
+      int4* d4 = reinterpret_cast<int4*>(dst);
+      for (int v = lane; v < nv; v += 32 * 4) {
+        int4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v + u * 32 < nv) r[u] = __ldcg(s4 + v + u * 32);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (v + u * 32 < nv) {
+            TIn* e = reinterpret_cast<TIn*>(&r[u]);
+            int4 o;
+            TOut* eo = reinterpret_cast<TOut*>(&o);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) eo[j] = from_f32<TOut>(to_f32(e[j]) * scale);
+            d4[v + u * 32] = o;
+          }
+        }
+      }
+    } else {
+      for (int h = lane; h < hidden; h += 32) dst[h] = from_f32<TOut>(to_f32(src[h]) * scale);
+    }
   }
 }
 

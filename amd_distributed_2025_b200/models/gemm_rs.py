@@ -64,6 +64,7 @@ class GemmRS:
         )
         self.max_ctas = 0  # 0 = one CTA per SM
         self.block_n = 0  # 0 = tile width chosen from the shape (64 / 128 / 256)
+        self.cta_pair = -1  # -1 = chosen from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
 
     def __call__(
         self,
@@ -84,20 +85,24 @@ class GemmRS:
             out = torch.empty((m // self.world_size, n), dtype=torch.bfloat16, device=a.device)
         epoch = self.ws.next_epoch("gemm_rs")
         parity = epoch & 1
-        bias_scale = float(self.world_size) if bias_mode == "per_rank" else 1.0
+        # "per_rank": every rank adds the bias to its rounded partial before the reduction
+        # (the reference's order of operations); "once": the owner adds it after the sum.
+        at_source = bias_mode == "per_rank"
         self.ext.gemm_rs(
             self.ws.heap,
             a.contiguous(),
             w.contiguous(),
             bias,
             out,
-            bias_scale,
+            1.0,
+            at_source,
             self.ws.offset(f"stage{parity}"),
             self.ws.offset(f"counters{parity}"),
             epoch,
             self.ws.wait_limit_ns,
             self.max_ctas,
             self.block_n,
+            self.cta_pair,
         )
         return out
 

@@ -213,6 +213,34 @@ def gemm_rs_reference_rounding(
     return acc
 
 
+def gemm_rs_fused_rounding(
+    inputs: Sequence[torch.Tensor],
+    weights: Sequence[torch.Tensor],
+    bias: Optional[torch.Tensor],
+    rank: int,
+    *,
+    bias_mode: str = "per_rank",
+) -> torch.Tensor:
+    """The fused kernel's rounding points.  Every rank's partial is rounded to bf16 (as the
+    reference's matmul output is); with ``bias_mode="per_rank"`` the bf16 bias is added to
+    it and the sum rounded again, exactly as the reference does on every rank; the
+    partials are then summed in fp32 in rank order and rounded once (``"once"`` adds the
+    bias to that fp32 sum instead)."""
+    ws = len(inputs)
+    rows = inputs[0].shape[0] // ws
+    sl = slice(rank * rows, (rank + 1) * rows)
+    acc = None
+    for a, w in zip(inputs, weights):
+        part = (a[sl].to(torch.float32) @ w.to(torch.float32).T).to(torch.bfloat16)
+        if bias is not None and bias_mode == "per_rank":
+            part = part + bias
+        part = part.to(torch.float32)
+        acc = part if acc is None else acc + part
+    if bias is not None and bias_mode != "per_rank":
+        acc = acc + bias.to(torch.float32)
+    return acc.to(torch.bfloat16)
+
+
 def check_gemm_rs_output(
     output: torch.Tensor, expected: torch.Tensor, rtol: float = GEMM_RS_RTOL, atol: float = GEMM_RS_ATOL
 ) -> Tuple[bool, str]:
@@ -226,6 +254,16 @@ def check_gemm_rs_output(
         err = (output.float() - expected.float()).abs().max().item()
         return False, f"Output values mismatch, max abs err {err:.4g}"
     return True, ""
+
+
+def outlier_fraction(output: torch.Tensor, expected: torch.Tensor, rtol: float, atol: float) -> float:
+    """Share of elements outside ``atol + rtol * |expected|``.  With unit-variance operands
+    two correct bf16 implementations differ by an output ulp wherever an fp32 partial sits
+    on a rounding boundary, and an ulp exceeds the task tolerance for |y| in [4, 5.25), so
+    a strict ``allclose`` is replaced by a bound on this share for such inputs."""
+    diff = (output.to(torch.float32) - expected.to(torch.float32)).abs()
+    tol = atol + rtol * expected.to(torch.float32).abs()
+    return float((diff > tol).to(torch.float32).mean())
 
 
 def relative_error(output: torch.Tensor, truth: torch.Tensor) -> float:

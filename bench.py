@@ -32,7 +32,6 @@ import json
 import os
 import socket
 import statistics
-import subprocess
 import sys
 import time
 from typing import Any, Callable, Dict, List, Optional, Tuple
@@ -46,70 +45,10 @@ import torch.distributed as dist  # noqa: E402
 
 from amd_distributed_2025_b200 import contract  # noqa: E402
 from amd_distributed_2025_b200.utils import timing  # noqa: E402
+from amd_distributed_2025_b200.utils.clocks import ClockSampler  # noqa: E402
 
 METRIC = "dispatch+combine us, GEMM-RS us (max over ranks), geomean over headline configs"
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
-
-
-# --------------------------------------------------------------------------------------
-# clocks
-# --------------------------------------------------------------------------------------
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-        "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
-    )
-
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc: Optional[subprocess.Popen] = None
-
-    def start(self) -> None:
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
-            )
-        except OSError:
-            self.proc = None
-
-    def stop(self) -> Dict[str, Any]:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, smax, power, reasons = [], [], [], set()
-        for line in out.splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [c for c, p in zip(sm, power) if p > 0.5 * max(power)] or sm
-        return {
-            "sm_mhz": statistics.median(busy),
-            "sm_max_mhz": max(smax),
-            "power_w_max": max(power),
-            "samples": len(sm),
-            "reasons": sorted(reasons),
-        }
 
 
 # --------------------------------------------------------------------------------------

@@ -67,25 +67,29 @@ def test_moe_dispatch_combine_multi_rank(ws):
 
 
 GEMM_SHAPES = [
-    # (m, n, k, has_bias, seed) -- task test shapes plus small/ragged ones
-    (64, 2880, 2880, True, 2035),
-    (512, 3584, 14336, True, 4297),
-    (2048, 4096, 7168, False, 716),
-    (4096, 2880, 2880, True, 136),
-    (256, 5120, 12800, True, 61),
-    (8192, 8192, 28672, False, 1536),
+    # (m, n, k, has_bias, seed, operand distribution) -- task test shapes plus small/ragged ones
+    (64, 2880, 2880, True, 2035, "reference"),
+    (512, 3584, 14336, True, 4297, "reference"),
+    (2048, 4096, 7168, False, 716, "reference"),
+    (64, 2880, 2880, True, 2035, "normal"),
+    (512, 3584, 14336, True, 4297, "normal"),
+    (4096, 2880, 2880, True, 136, "normal"),
+    (256, 5120, 12800, True, 61, "normal"),
+    (8192, 8192, 28672, False, 1536, "normal"),
 ]
 
 
 def _gemm_rank(rank, world_size, shapes, repeats):
     from amd_distributed_2025_b200.models import gemm_rs
+    from amd_distributed_2025_b200.parallel.baseline_nccl import gemm_rs_torch
 
     dev = torch.device("cuda", torch.cuda.current_device())
     out = []
-    for (m, n, k, has_bias, seed) in shapes:
+    for (m, n, k, has_bias, seed, kind) in shapes:
         if m % world_size or k % world_size or (k // world_size) % 8:
             continue
-        everyone = [contract.make_gemm_rs_inputs(r, world_size, m, n, k, has_bias, seed, device=dev) for r in range(world_size)]
+        everyone = [contract.make_gemm_rs_inputs(r, world_size, m, n, k, has_bias, seed, device=dev, dist=kind)
+                    for r in range(world_size)]
         data = everyone[rank]
         for _ in range(repeats):  # alternating staging parities, no barrier in between
             y = gemm_rs.custom_kernel(data)
@@ -95,10 +99,20 @@ def _gemm_rank(rank, world_size, shapes, repeats):
             gemm_rs.get_op(m, n).check()
         except Exception as exc:  # noqa: BLE001
             ok, msg = False, str(exc)
-        truth = oracle.gemm_rs_truth([e[0] for e in everyone], [e[1] for e in everyone], data[2], rank, dtype=torch.float32)
-        ok2, msg2 = oracle.check_gemm_rs_output(y, truth.to(y.dtype))
+        a_all, w_all = [e[0] for e in everyone], [e[1] for e in everyone]
+        truth = oracle.gemm_rs_truth(a_all, w_all, data[2], rank, dtype=torch.float32)
         rel = oracle.relative_error(y, truth)
-        out.append({"shape": [m, n, k], "ok": bool(ok and ok2 and rel < 1e-2), "msg": msg or msg2, "rel": rel})
+        lib = gemm_rs_torch(data)  # library GEMM + NCCL reduce-scatter: what the task's checker computes
+        if kind == "reference":
+            ok2, msg2 = oracle.check_gemm_rs_output(y, lib)
+            outliers = 0.0
+        else:
+            want = oracle.gemm_rs_fused_rounding(a_all, w_all, data[2], rank)
+            outliers = max(oracle.outlier_fraction(y, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL),
+                           oracle.outlier_fraction(y, lib, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL))
+            ok2, msg2 = outliers < 1e-3, f"{outliers:.2e} of the elements outside the task tolerance"
+        out.append({"shape": [m, n, k, kind], "ok": bool(ok and ok2 and rel < 5e-3), "msg": msg or msg2, "rel": rel,
+                    "outliers": outliers})
         del everyone
     return out
 
@@ -108,4 +122,4 @@ def test_gemm_rs_multi_rank(ws):
     for per_rank in run_ranks(_gemm_rank, ws, "nccl", (GEMM_SHAPES, 4), 900.0):
         assert per_rank, "no shape ran"
         for r in per_rank:
-            assert r["ok"], (r["shape"], r["msg"], r["rel"])
+            assert r["ok"], (r["shape"], r["msg"], r["rel"], r["outliers"])
