@@ -176,7 +176,8 @@ void moe_combine(SymmHeap& heap, at::Tensor out, const at::Tensor& weights, cons
 
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
              at::Tensor out, double bias_scale, bool bias_at_source, int64_t off_stage, int64_t off_counters, int64_t epoch,
-             int64_t timeout_ns, int64_t max_ctas, int64_t block_n, int64_t cta_pair) {
+             int64_t timeout_ns, int64_t max_ctas, int64_t block_n, int64_t cta_pair, int64_t splits,
+             const c10::optional<at::Tensor>& trace) {
   TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
               "input and weight must be bf16 CUDA tensors");
@@ -216,6 +217,13 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.max_ctas = (int)max_ctas;
   g.block_n = (int)block_n;
   g.cta_pair = (int)cta_pair;
+  g.splits = (int)splits;
+  g.trace = nullptr;
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 4 * 160,
+                "trace must be a contiguous int64 tensor with at least 640 elements");
+    g.trace = reinterpret_cast<uint64_t*>(trace->data_ptr<int64_t>());
+  }
   cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
 }
 
@@ -269,8 +277,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_expert_scale", &moe_expert_scale);
   m.def("moe_combine", &moe_combine);
   m.def("gemm_rs", &gemm_rs);
-  m.def("gemm_rs_workspace_bytes", [](int64_t M, int64_t N, int64_t ws) {
-    return py::make_tuple((int64_t)b200::gemm_rs_stage_bytes((int)M, (int)N, (int)ws),
-                          (int64_t)b200::gemm_rs_counter_bytes((int)M, (int)N, (int)ws));
+  m.def("gemm_rs_plan", [](int64_t M, int64_t N, int64_t K, int64_t ws, int64_t block_n, int64_t cta_pair, int64_t splits) {
+    const b200::GemmRsPlan p = b200::gemm_rs_plan((int)M, (int)N, (int)K, (int)ws, (int)block_n, (int)cta_pair, (int)splits);
+    py::dict d;
+    d["block_n"] = p.block_n;
+    d["cta_pair"] = p.cta_pair;
+    d["splits"] = p.splits;
+    d["stage_bytes"] = (int64_t)p.stage_bytes;
+    d["counter_bytes"] = (int64_t)p.counter_bytes;
+    return d;
   });
 }

@@ -45,11 +45,19 @@ struct GemmRsArgs {
   int max_ctas;  // 0 = one per SM
   int block_n;   // 0 = choose from the shape; else 64, 128 or 256
   int cta_pair;  // -1 = choose from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
+  int splits;    // 0 = choose from the shape; else the number of K slices per tile
+  uint64_t* trace;  // optional device buffer [CTAs][4] of globaltimer stamps (start, pipeline ready,
+                    // GEMM tiles done, exit); nullptr = no tracing
 };
 
-// Bytes of ONE parity of the staging buffer / the counters for a problem.
-uint64_t gemm_rs_stage_bytes(int M, int N, int world_size);
-uint64_t gemm_rs_counter_bytes(int M, int N, int world_size);
+// How a problem will be run, and what ONE parity of its workspace needs.  A pure function of
+// its arguments (and the SM count), so every rank derives the same plan.
+struct GemmRsPlan {
+  int block_n, cta_pair, splits;
+  uint64_t stage_bytes;    // bf16 [world * splits][M / world][N]
+  uint64_t counter_bytes;  // uint32 [m_tiles][n_tiles][4]
+};
+GemmRsPlan gemm_rs_plan(int M, int N, int K, int world_size, int block_n, int cta_pair, int splits);
 
 cudaError_t launch_gemm_rs(const GemmRsArgs& args, cudaStream_t stream);
 

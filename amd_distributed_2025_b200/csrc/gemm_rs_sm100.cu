@@ -47,18 +47,20 @@ struct Cfg {
   static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTxBytes = CTAS * kStageBytes;   // bytes counted on the (leader's) full barrier
-  static constexpr int kEpiCols = BN < 128 ? BN : 128;  // columns transposed at a time
+  static constexpr int kEpiCols = (BN % 128 == 0) ? 128 : 64;  // columns transposed at a time
   static constexpr int kSlabBytes = 32 * kEpiCols * 2;  // per epilogue warp
   static constexpr int kEpiBytes = kEpilogueWarps * kSlabBytes;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kStagesRaw = (kSmemLimit - 1024 - kEpiBytes - kBarrierBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two >= 32
+  static constexpr int kAccStride = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);  // TMEM columns per accumulator
+  static constexpr int kTmemCols = 2 * kAccStride;                             // two accumulators; power of two
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
   static_assert(kStages >= 3, "pipeline too shallow");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   static_assert(kBRows % 8 == 0 && kBRows <= 256, "W box rows");
+  static_assert(BN % kEpiCols == 0 && BN % 16 == 0 && BN <= 256, "tile width");
 };
 
 struct KernelParams {
@@ -69,13 +71,23 @@ struct KernelParams {
   int m_tiles, n_tiles, num_kb;  // m_tiles counts 128-row blocks
   int m_groups;  // row groups of 128 * CTAS rows: the scheduling unit along M
   int m_start;   // first row group of the rotated order (the one after this rank's rows)
+  int band;      // row groups visited together, column tile by column tile, so that concurrently
+                 // running tiles share A and W tiles in L2
+  int splits;    // K is cut into this many slices per tile; each slice is one work item whose
+                 // bf16 partial is staged like a rank's partial ("virtual ranks")
+  int kb_per_split;
   float bias_scale;
   int bias_at_source;  // 1: every rank adds the bias to its rounded partial (the reference's order of operations)
   uint64_t peer_base[kMaxWorldSize];
   uint64_t off_stage, off_counters;
   uint64_t epoch, timeout_ns;
   StatusBlock* status;
+  uint64_t* trace;  // optional [gridDim.x][4] globaltimer stamps: start, pipeline ready, GEMM tiles done, exit
 };
+
+__device__ __forceinline__ void trace_stamp(const KernelParams& p, int slot) {
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * 4 + slot] = global_timer_ns();
+}
 
 struct PipeState {
   uint32_t stage = 0, phase = 0;
@@ -112,22 +124,30 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Work item t of this CTA (pair): row group (rotated so the rank's own rows come last) and
-// column tile; `mb` is the 128-row block this CTA computes.
+// Work item t of this CTA (pair): K slice, row group (rotated so the rank's own rows come
+// last, visited in bands) and column tile; `mb` is the 128-row block this CTA computes.
 template <int CTAS>
-__device__ __forceinline__ void tile_coords(const KernelParams& p, int t, uint32_t cta_rank, int& mb, int& nb) {
-  const int j = t / p.n_tiles;
-  nb = t - j * p.n_tiles;
-  int mg = p.m_start + j;
+__device__ __forceinline__ void tile_coords(const KernelParams& p, int t, uint32_t cta_rank, int& mb, int& nb,
+                                            int& split) {
+  const int tile = t / p.splits;
+  split = t - tile * p.splits;
+  const int per_band = p.band * p.n_tiles;
+  const int b = tile / per_band;
+  const int start = b * p.band;
+  const int size = min(p.band, p.m_groups - start);
+  const int within = tile - start * p.n_tiles;
+  nb = within / size;
+  int mg = p.m_start + start + (within - nb * size);
   if (mg >= p.m_groups) mg -= p.m_groups;
   mb = mg * CTAS + (int)cta_rank;
 }
 
-// True when every row of m-tile `mb` belongs to this rank (and lies inside M).
+// True when every row of m-tile `mb` belongs to this rank (and lies inside M) and K is not
+// sliced: such a tile is finished in the epilogue of the rank itself.
 __device__ __forceinline__ bool tile_owned(const KernelParams& p, int mb) {
   const int lo = mb * BM;
   const int row_lo = p.rank * p.rows_per_rank;
-  return lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
+  return p.splits == 1 && lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
 }
 
 // Sum of the world_size bf16 partial vectors of out[rl, n..n+8) in rank order, in fp32,
@@ -139,12 +159,13 @@ __device__ __forceinline__ uint4 reduce_partials(const KernelParams& p, const __
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   const size_t R = (size_t)p.rows_per_rank;
-  for (int s0 = 0; s0 < p.world_size; s0 += 8) {
+  const int sources = p.world_size * p.splits;
+  for (int s0 = 0; s0 < sources; s0 += 8) {
     uint4 vals[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int s = s0 + u;
-      if (s < p.world_size) {
+      if (s < sources) {
         if (own != nullptr && s == p.rank) vals[u] = *own;
         else vals[u] = __ldcg(reinterpret_cast<const uint4*>(stage + ((size_t)s * R + rl) * p.N + n));
       } else {
@@ -180,6 +201,72 @@ __device__ __forceinline__ uint4 reduce_partials(const KernelParams& p, const __
   return o;
 }
 
+// Reduce `items` 16-byte vectors of the block rows [r0, ...) x columns [c0, c0 + 8 * vec_per_row)
+// with the whole CTA.  Every thread keeps 8 vectors per source in flight (the reduction is
+// latency-bound otherwise), adds sources in (virtual) rank order in fp32, rounds once.
+__device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_bfloat16* stage, int r0, int row_lo,
+                                             int c0, int vec_per_row, int items, int tid) {
+  constexpr int U = 8;
+  const size_t R = (size_t)p.rows_per_rank;
+  const int sources = p.world_size * p.splits;
+  for (int base = tid; base < items; base += kThreads * U) {
+    float acc[U][8];
+    size_t off[U];  // element offset of the vector inside one source's [R, N] block; ~0 = past the end
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * kThreads;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      if (i < items) {
+        const int rl = r0 + i / vec_per_row - row_lo;
+        const int n = c0 + ((i % vec_per_row) << 3);
+        off[u] = (size_t)rl * p.N + n;
+      } else {
+        off[u] = ~(size_t)0;
+      }
+    }
+    for (int s = 0; s < sources; ++s) {
+      const __nv_bfloat16* src = stage + (size_t)s * R * p.N;
+      uint4 vals[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        vals[u] = off[u] != ~(size_t)0 ? __ldcg(reinterpret_cast<const uint4*>(src + off[u])) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[u][2 * e] += f.x;
+          acc[u][2 * e + 1] += f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (off[u] == ~(size_t)0) continue;
+      if (p.bias != nullptr && !p.bias_at_source) {
+        const int n = (int)(off[u] % (size_t)p.N);
+        const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[u][2 * e] = fmaf(f.x, p.bias_scale, acc[u][2 * e]);
+          acc[u][2 * e + 1] = fmaf(f.y, p.bias_scale, acc[u][2 * e + 1]);
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+      o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+      o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+      o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+      *reinterpret_cast<uint4*>(p.out + off[u]) = o;
+    }
+  }
+}
+
 }  // namespace
 
 template <int BN, int CTAS>
@@ -195,6 +282,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  trace_stamp(p, 0);
   const uint32_t cta_rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
 
@@ -238,8 +326,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (CTAS == 2) ptx::cluster_sync_all();  // the peer's barriers exist before anything signals them
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_shared;
+  trace_stamp(p, 1);
 
-  const int total_tiles = p.m_groups * p.n_tiles;
+  const int total_tiles = p.m_groups * p.n_tiles * p.splits;
   const int G = gridDim.x;              // CTAs
   const int GG = G / CTAS;              // CTAs or CTA pairs: the schedulers
   const int gidx = (int)blockIdx.x / CTAS;
@@ -251,9 +340,11 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     if (lane == 0) {
       PipeState ps;
       for (int t = gidx; t < total_tiles && !abort_flag; t += GG) {
-        int mb, nb;
-        tile_coords<CTAS>(p, t, cta_rank, mb, nb);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        int mb, nb, split;
+        tile_coords<CTAS>(p, t, cta_rank, mb, nb, split);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, &abort_flag, limit, p.status, 100 + (int)ps.stage)) break;
           const uint32_t sa = smem_a0 + ps.stage * C::kStageBytes;
           const uint32_t sb = sa + C::kABytes;
@@ -282,9 +373,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, limit, p.status, 200 + (int)acc)) break;
         ptx::tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + acc * C::kAccStride;
+        const int split = t % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         bool ok = true;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(ps.stage), ps.phase, &abort_flag, limit, p.status, 300 + (int)ps.stage)) {
             ok = false;
             break;
@@ -297,8 +391,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j) {
             // advancing K by 16 bf16 = 32 bytes = 2 descriptor address units
-            if (CTAS == 2) ptx::umma_bf16_pair(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-            else ptx::umma_bf16(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            if (CTAS == 2) ptx::umma_bf16_pair(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            else ptx::umma_bf16(tmem_d, da + 2u * j, db + 2u * j, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
           // stage reusable (in both CTAs of a pair) once these MMAs have read it
           if (CTAS == 2) ptx::umma_commit_pair(empty_bar(ps.stage), 3);
@@ -318,15 +412,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     constexpr int kChunksPerRow = C::kEpiCols / 8;       // 16-byte chunks per slab row
     constexpr int kRowsPerStore = 32 / kChunksPerRow;    // slab rows covered by one warp store
     constexpr int kRowPitch = C::kEpiCols * 2;
-    const bool direct = (p.world_size == 1);
+    const bool direct = (p.world_size == 1 && p.splits == 1);
     const int R = p.rows_per_rank;
     const int row_lo = p.rank * R;
     uint32_t* my_counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
     const __nv_bfloat16* my_stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
     uint32_t it = 0;
     for (int t = gidx; t < total_tiles && !abort_flag; t += GG, ++it) {
-      int mb, nb;
-      tile_coords<CTAS>(p, t, cta_rank, mb, nb);
+      int mb, nb, split;
+      tile_coords<CTAS>(p, t, cta_rank, mb, nb, split);
       const uint32_t acc = it & 1u;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, limit, p.status, 400 + (int)acc)) break;
@@ -344,10 +438,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < C::kEpiCols / 32; ++c) {
           uint32_t v[32];
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * C::kEpiCols + c * 32;
+          const uint32_t taddr =
+              tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::kAccStride + half * C::kEpiCols + c * 32;
           ptx::tmem_ld_32x32b_x32(taddr, v);
           ptx::tmem_ld_wait();
-          if (p.bias != nullptr && (direct || p.bias_at_source)) {
+          // with K slices, only slice 0 of a rank carries that rank's bias
+          if (p.bias != nullptr && (direct || (p.bias_at_source && split == 0))) {
             const int nbase = n0 + half * C::kEpiCols + c * 32;
             if (p.bias_at_source) {
               // reference order: round the product to bf16, add the bf16 bias, round again
@@ -430,7 +526,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               const int owner = m / R;
               const int rl = m - owner * R;
               __nv_bfloat16* dst = peer_ptr<__nv_bfloat16>(p.peer_base[owner], p.off_stage) +
-                                   ((size_t)p.rank * R + rl) * p.N + n;
+                                   ((size_t)(p.rank * p.splits + split) * R + rl) * p.N + n;
               *reinterpret_cast<uint4*>(dst) = val;
             }
           }
@@ -441,15 +537,22 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (lane == 0) my_counters[ctr_index] = 0;  // next used by the call after next
       } else if (!direct) {
         // Tell every owner with rows in this tile that warp q's 32 rows have been stored.
+        // Device scope is enough (and much cheaper) when the only owner is this GPU.
         __syncwarp();
         if (lane == 0) {
-          __threadfence_system();
           const int m_lo = mb * BM;
           const int m_hi = min(p.M, m_lo + BM) - 1;
           const int o_lo = m_lo / R;
           const int o_hi = m_hi / R;
-          for (int o = o_lo; o <= o_hi; ++o) {
-            red_release_sys_add(peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + ctr_index, 1u);
+          if (o_lo <= o_hi) {
+            const bool local_only = (o_lo == p.rank && o_hi == p.rank);
+            if (local_only) __threadfence();
+            else __threadfence_system();
+            for (int o = o_lo; o <= o_hi; ++o) {
+              uint32_t* ctr = peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + ctr_index;
+              if (o == p.rank) red_release_gpu_add(ctr, 1u);
+              else red_release_sys_add(ctr, 1u);
+            }
           }
         }
       }
@@ -473,16 +576,23 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     if (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
     else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
-  if (p.world_size == 1 || abort_flag) return;
+  trace_stamp(p, 2);
+  if ((p.world_size == 1 && p.splits == 1) || abort_flag) {
+    trace_stamp(p, 3);
+    return;
+  }
 
-  // ================================ reduction of shared tiles =============================
+  // ================================ reduction of staged tiles =============================
   // Tiles that straddle an ownership boundary (always the case when a rank owns fewer than
-  // 128 rows) were staged by every rank, this one included.  Block j of them is reduced by
-  // CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles start first.
+  // 128 rows) and all tiles of a K-sliced problem were staged by every (virtual) rank, this
+  // one included.  The unit of work is one 128 x BN tile (four counters, one per 32-row
+  // quarter); unit j is reduced by CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles
+  // start first.
   const int R = p.rows_per_rank;
   const int row_lo = p.rank * R;
   const int mb_lo = row_lo / BM;
   const int mb_hi = (row_lo + R - 1) / BM;
+  const uint32_t want = (uint32_t)(p.world_size * p.splits);
   uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
   const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
   int j = 0;
@@ -490,37 +600,31 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     if (tile_owned(p, mb)) continue;
     for (int nb = 0; nb < p.n_tiles; ++nb, ++j) {
       if (j % G != G - 1 - (int)blockIdx.x) continue;
+      // one counter per 32-row quarter of the tile: four threads wait in parallel
       uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps;
-      if (tid == 0) {
-        int ok = 1;
-        for (int w = 0; w < kEpilogueWarps && ok; ++w) {
-          ok = wait_u32_ge(ctr + w, (uint32_t)p.world_size, limit, p.status, PHASE_RS_PARTIALS, -1,
-                           mb * p.n_tiles + nb, true)
-                   ? 1
-                   : 0;
-        }
-        wait_ok_shared = ok;
+      if (tid == 0) wait_ok_shared = 1;
+      __syncthreads();
+      if (tid < kEpilogueWarps) {
+        if (!wait_u32_ge(ctr + tid, want, limit, p.status, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb,
+                         p.world_size > 1))
+          wait_ok_shared = 0;
       }
       __syncthreads();
       const bool ok = wait_ok_shared != 0;
-      if (ok) {
-        const int r0 = max(mb * BM, row_lo);
-        const int r1 = min(min((mb + 1) * BM, row_lo + R), p.M);
+      const int r0 = max(mb * BM, row_lo);
+      const int r1 = min(min((mb + 1) * BM, row_lo + R), p.M);
+      if (ok && r1 > r0) {
         const int c0 = nb * BN;
         const int c1 = min(c0 + BN, p.N);
         const int vec_per_row = (c1 - c0) >> 3;
-        const int items = (r1 - r0) * vec_per_row;
-        for (int i = tid; i < items; i += kThreads) {
-          const int rl = r0 + i / vec_per_row - row_lo;
-          const int n = c0 + ((i % vec_per_row) << 3);
-          *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) = reduce_partials(p, stage, rl, n, nullptr);
-        }
+        reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
       }
       __syncthreads();
       if (tid < kEpilogueWarps) ctr[tid] = 0;  // this parity's counters are next used two calls from now
       if (!ok) return;
     }
   }
+  trace_stamp(p, 3);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -561,31 +665,53 @@ bool make_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS;
 }
 
-// Tile shape from the problem size: CTA pairs with 256-row tiles once the problem fills the
-// machine, single CTAs with narrower tiles for small problems.
-void pick_config(int M, int N, int sms, int& bn, int& ctas) {
+// Tile shape and K slicing from the problem size.  Cost model: waves of work items times
+// the time of one item (proportional to its k-blocks and its width, with a penalty for
+// narrow tiles, which use the tensor pipe less well).
+GemmRsPlan make_plan(int M, int N, int K, int world_size, int sms, int force_bn, int force_pair, int force_splits) {
   const int m_tiles = (M + BM - 1) / BM;
-  const int pairs = sms / 2;
-  for (int cand : {256, 128}) {
-    const int tiles = ((m_tiles + 1) / 2) * ((N + cand - 1) / cand);
-    if (tiles >= pairs) {
-      bn = cand;
-      ctas = 2;
-      return;
+  const int num_kb = (K + BK - 1) / BK;
+  GemmRsPlan best = {};
+  double best_cost = 1e300;
+  struct Cand { int bn, ctas; double penalty; };
+  const Cand cands[] = {{256, 2, 1.0}, {192, 2, 1.06}, {128, 2, 1.5}, {256, 1, 1.18}, {128, 1, 1.55}, {64, 1, 2.9}};
+  for (const Cand& c : cands) {
+    if (force_bn > 0 && c.bn != force_bn) continue;
+    if (force_pair >= 0 && (c.ctas == 2) != (force_pair != 0)) continue;
+    const int schedulers = std::max(sms / c.ctas, 1);
+    const int tiles = ((m_tiles + c.ctas - 1) / c.ctas) * ((N + c.bn - 1) / c.bn);
+    int max_splits = 1;
+    if (force_splits > 0) max_splits = force_splits;
+    else if (tiles * 2 <= schedulers) max_splits = std::min(std::min(schedulers / tiles, num_kb / 4), 8);
+    for (int sp = (force_splits > 0 ? force_splits : 1); sp <= std::max(max_splits, 1); ++sp) {
+      int per = (num_kb + sp - 1) / sp;
+      if ((sp - 1) * per >= num_kb) continue;  // an empty slice
+      const double waves = std::ceil((double)tiles * sp / schedulers);
+      // Item time in units of (k-blocks x columns); 1536 stands for the fixed ramp-up and
+      // epilogue of an item, 400 per slice for staging and re-reading the partial tile.
+      const double cost = waves * (per * c.bn * c.penalty + 1536.0) + (sp > 1 ? 400.0 * sp : 0.0);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.block_n = c.bn;
+        best.cta_pair = c.ctas == 2 ? 1 : 0;
+        best.splits = sp;
+      }
     }
   }
-  ctas = 1;
-  for (int cand : {128}) {
-    if (m_tiles * ((N + cand - 1) / cand) >= sms) {
-      bn = cand;
-      return;
-    }
+  if (best.block_n == 0) {
+    best.block_n = force_bn > 0 ? force_bn : 128;
+    best.cta_pair = 0;
+    best.splits = 1;
   }
-  bn = 64;
+  best.stage_bytes = (uint64_t)best.splits * (uint64_t)M * (uint64_t)N * 2ull;
+  const uint64_t n_tiles = (N + 63) / 64;
+  best.counter_bytes = ((uint64_t)m_tiles * n_tiles * kEpilogueWarps * 4 + 255) / 256 * 256;
+  (void)world_size;
+  return best;
 }
 
 template <int BN, int CTAS>
-cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
+cudaError_t launch_typed(const GemmRsArgs& a, int sms, int splits, cudaStream_t stream) {
   using C = Cfg<BN, CTAS>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map(&map_a, a.a, (uint64_t)a.M, (uint64_t)a.K, BM)) return cudaErrorInvalidValue;
@@ -607,6 +733,11 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
   // rotated order: start with the first row group wholly after this rank's rows
   const int64_t group_rows = (int64_t)BM * CTAS;
   p.m_start = (int)((((int64_t)(a.rank + 1) * p.rows_per_rank + group_rows - 1) / group_rows) % p.m_groups);
+  p.splits = splits;
+  p.kb_per_split = (p.num_kb + splits - 1) / splits;
+  // bands of up to 8 row groups, never mixing a rank's own rows into a band that starts elsewhere
+  const int groups_per_rank = std::max((int)(p.rows_per_rank / group_rows), 1);
+  p.band = std::max(1, std::min(std::min(8, groups_per_rank), p.m_groups));
   p.bias_scale = a.bias_scale;
   p.bias_at_source = a.bias_at_source;
   for (int r = 0; r < kMaxWorldSize; ++r) p.peer_base[r] = a.peer_base[r];
@@ -615,18 +746,21 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
   p.epoch = a.epoch;
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
+  p.trace = a.trace;
 
   auto kernel = gemm_rs_kernel<BN, CTAS>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  if (e != cudaSuccess) return e;
-
-  const int total = p.m_groups * p.n_tiles;
-  int schedulers = std::min(total, sms / CTAS);
-  if (a.max_ctas > 0) schedulers = std::min(schedulers, std::max(a.max_ctas / CTAS, 1));
-  if (schedulers < 1) schedulers = 1;
+  // Per kernel variant and device, once: opt in to the large dynamic shared memory and ask
+  // how many CTA pairs can be resident (both calls are slow enough to matter per launch).
+  struct VariantInfo {
+    bool ready = false;
+    int max_clusters = 0;
+  };
+  static VariantInfo info[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  VariantInfo& vi = info[dev & 63];
 
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(schedulers * CTAS));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
@@ -637,29 +771,33 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (CTAS == 2 && a.max_ctas <= 0) {
-    // never launch more pairs than can be resident at once
-    int max_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) == cudaSuccess && max_clusters > 0 &&
-        max_clusters < schedulers) {
-      cfg.gridDim = dim3((unsigned)(max_clusters * CTAS));
+  if (!vi.ready) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    vi.max_clusters = sms / CTAS;
+    if (CTAS == 2) {
+      cfg.gridDim = dim3((unsigned)(sms / CTAS * CTAS));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0) vi.max_clusters = std::min(n, sms / CTAS);
     }
+    vi.ready = true;
   }
+
+  const int total = p.m_groups * p.n_tiles * splits;
+  int schedulers = std::min(total, vi.max_clusters);  // never more CTAs (pairs) than can be resident at once
+  if (a.max_ctas > 0) schedulers = std::min(schedulers, std::max(a.max_ctas / CTAS, 1));
+  if (schedulers < 1) schedulers = 1;
+  cfg.gridDim = dim3((unsigned)(schedulers * CTAS));
   return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
 }
 
 }  // namespace
 
-uint64_t gemm_rs_stage_bytes(int M, int N, int world_size) {
-  (void)world_size;
-  return (uint64_t)M * (uint64_t)N * 2ull;  // world * (M / world) * N bf16
-}
-
-uint64_t gemm_rs_counter_bytes(int M, int N, int world_size) {
-  (void)world_size;
-  const uint64_t m_tiles = (M + BM - 1) / BM;
-  const uint64_t n_tiles = (N + 63) / 64;
-  return (m_tiles * n_tiles * kEpilogueWarps * 4 + 255) / 256 * 256;
+GemmRsPlan gemm_rs_plan(int M, int N, int K, int world_size, int block_n, int cta_pair, int splits) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  return make_plan(M, N, K, world_size, sms, block_n, cta_pair, splits);
 }
 
 cudaError_t launch_gemm_rs(const GemmRsArgs& a, cudaStream_t stream) {
@@ -668,22 +806,20 @@ cudaError_t launch_gemm_rs(const GemmRsArgs& a, cudaStream_t stream) {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int bn = 0, ctas = 0;
-  pick_config(a.M, a.N, sms, bn, ctas);
-  if (a.block_n > 0) bn = a.block_n;
-  if (a.cta_pair >= 0) ctas = a.cta_pair ? 2 : 1;
-  if (ctas == 2 && bn == 64) ctas = 1;
-  if (ctas == 2) {
-    switch (bn) {
-      case 256: return launch_typed<256, 2>(a, sms, stream);
-      case 128: return launch_typed<128, 2>(a, sms, stream);
+  const GemmRsPlan plan = make_plan(a.M, a.N, a.K, a.world_size, sms, a.block_n, a.cta_pair, a.splits);
+  const int sp = plan.splits;
+  if (plan.cta_pair) {
+    switch (plan.block_n) {
+      case 256: return launch_typed<256, 2>(a, sms, sp, stream);
+      case 192: return launch_typed<192, 2>(a, sms, sp, stream);
+      case 128: return launch_typed<128, 2>(a, sms, sp, stream);
       default: return cudaErrorInvalidValue;
     }
   }
-  switch (bn) {
-    case 256: return launch_typed<256, 1>(a, sms, stream);
-    case 128: return launch_typed<128, 1>(a, sms, stream);
-    case 64: return launch_typed<64, 1>(a, sms, stream);
+  switch (plan.block_n) {
+    case 256: return launch_typed<256, 1>(a, sms, sp, stream);
+    case 128: return launch_typed<128, 1>(a, sms, sp, stream);
+    case 64: return launch_typed<64, 1>(a, sms, sp, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -8,9 +8,11 @@ expects ``world_size * bias``; ``bias_mode="per_rank"`` (default) reproduces tha
 ``"once"`` adds the bias a single time.
 
 ``GemmRS`` owns the symmetric workspace of the fused kernel (csrc/gemm_rs_sm100.cu): two
-parities of a bf16 staging buffer ``[world][M/ws][N]`` that peers store partial rows into
-and two parities of per-tile arrival counters.  Calls alternate parity, which is what
-lets consecutive calls overlap safely without any barrier between them.
+parities of a bf16 staging buffer ``[world * splits][M/ws][N]`` that peers store partial
+rows into and two parities of per-tile arrival counters.  Calls alternate parity, which
+is what lets consecutive calls run back to back without a barrier: a rank can only reach
+call ``n + 2`` after it has received every peer's partials of call ``n + 1``, so every
+peer has started call ``n + 1`` and therefore finished reading parity ``n % 2``.
 """
 from __future__ import annotations
 
@@ -24,8 +26,7 @@ from ..parallel.baseline_nccl import gemm_rs_torch
 from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace
 
 
-def gemm_rs_slab_layout(max_m: int, max_n: int, world_size: int, header_bytes: int, ext) -> SlabLayout:
-    stage_bytes, counter_bytes = ext.gemm_rs_workspace_bytes(max_m, max_n, world_size)
+def gemm_rs_slab_layout(stage_bytes: int, counter_bytes: int, header_bytes: int) -> SlabLayout:
     lay = SlabLayout(header_bytes)
     lay.add("counters0", counter_bytes)
     lay.add("counters1", counter_bytes)
@@ -35,10 +36,17 @@ def gemm_rs_slab_layout(max_m: int, max_n: int, world_size: int, header_bytes: i
 
 
 class GemmRS:
+    """Fused GEMM + reduce-scatter operator with a workspace of fixed capacity.
+
+    ``stage_bytes`` / ``counter_bytes`` are the capacity of ONE parity; ``plan(m, n, k)``
+    tells what a problem needs (tile shape, K slices, bytes).  ``block_n``, ``cta_pair``,
+    ``splits`` and ``max_ctas`` override the planner (0 / -1 = automatic).
+    """
+
     def __init__(
         self,
-        max_m: int,
-        max_n: int,
+        stage_bytes: int,
+        counter_bytes: int,
         rank: Optional[int] = None,
         world_size: Optional[int] = None,
         group=None,
@@ -51,9 +59,9 @@ class GemmRS:
         initialized = dist.is_available() and dist.is_initialized()
         self.world_size = world_size if world_size is not None else (dist.get_world_size(group) if initialized else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if initialized else 0)
-        self.max_m, self.max_n = int(max_m), int(max_n)
+        self.stage_bytes, self.counter_bytes = int(stage_bytes), int(counter_bytes)
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        layout = gemm_rs_slab_layout(self.max_m, self.max_n, self.world_size, self.ext.HEAP_HEADER_BYTES, self.ext)
+        layout = gemm_rs_slab_layout(self.stage_bytes, self.counter_bytes, self.ext.HEAP_HEADER_BYTES)
         self.ws = SymmetricWorkspace(
             layout,
             rank=self.rank,
@@ -63,8 +71,16 @@ class GemmRS:
             wait_limit_ms=wait_limit_ms,
         )
         self.max_ctas = 0  # 0 = one CTA per SM
-        self.block_n = 0  # 0 = tile width chosen from the shape (64 / 128 / 256)
+        self.block_n = 0  # 0 = tile width chosen from the shape (64 / 128 / 192 / 256)
         self.cta_pair = -1  # -1 = chosen from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
+        self.splits = 0  # 0 = chosen from the shape; else K slices per tile
+        self.trace: Optional[torch.Tensor] = None  # int64 [>=160, 4]: per-CTA globaltimer stamps when set
+
+    def plan(self, m: int, n: int, k: int) -> dict:
+        return self.ext.gemm_rs_plan(m, n, k, self.world_size, self.block_n, self.cta_pair, self.splits)
+
+    def fits(self, plan: dict) -> bool:
+        return plan["stage_bytes"] <= self.stage_bytes and plan["counter_bytes"] <= self.counter_bytes
 
     def __call__(
         self,
@@ -74,10 +90,10 @@ class GemmRS:
         bias_mode: str = "per_rank",
         out: Optional[torch.Tensor] = None,
     ) -> torch.Tensor:
-        m, n = a.shape[0], w.shape[0]
-        stage_bytes, counter_bytes = self.ext.gemm_rs_workspace_bytes(m, n, self.world_size)
-        if stage_bytes > self.ws.layout.size("stage0") or counter_bytes > self.ws.layout.size("counters0"):
-            raise ValueError(f"problem {m}x{n} exceeds the workspace capacity {self.max_m}x{self.max_n}")
+        m, n, k = a.shape[0], w.shape[0], a.shape[1]
+        plan = self.plan(m, n, k)
+        if not self.fits(plan):
+            raise ValueError(f"problem {m}x{n}x{k} needs {plan['stage_bytes']} staging bytes, workspace has {self.stage_bytes}")
         if bias_mode not in ("per_rank", "once"):
             raise ValueError("bias_mode must be 'per_rank' or 'once'")
         self.ws.check()
@@ -101,10 +117,17 @@ class GemmRS:
             epoch,
             self.ws.wait_limit_ns,
             self.max_ctas,
-            self.block_n,
-            self.cta_pair,
+            plan["block_n"],
+            plan["cta_pair"],
+            plan["splits"],
+            self.trace,
         )
         return out
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Record per-CTA phase time stamps (ns) of the next calls into ``self.trace``:
+        columns = kernel start, pipeline ready, GEMM tiles done, exit."""
+        self.trace = torch.zeros((160, 4), dtype=torch.int64, device=self.device) if on else None
 
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
@@ -116,22 +139,33 @@ class GemmRS:
 _OPS: Dict[tuple, GemmRS] = {}
 
 
-def get_op(m: int, n: int, group=None) -> GemmRS:
-    """Cached operator whose workspace fits ``[m, n]``; growing it is collective."""
+def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> GemmRS:
+    """Cached operator whose workspace fits the problem; growing it is collective.
+
+    The workspace is sized for ``splits_hint`` K slices of an ``m x n`` output when the
+    problem is small (so forcing more slices in experiments still fits), else for the plan.
+    """
+    from ..ops import _ext
+
+    ext = _ext.load()
     initialized = dist.is_available() and dist.is_initialized()
     ws = dist.get_world_size(group) if initialized else 1
     key = (ws, id(group), torch.cuda.current_device())
+    plan = ext.gemm_rs_plan(m, n, max(k, 64), ws, 0, -1, 0)
+    need_stage = plan["stage_bytes"]
+    if m * n * 2 * splits_hint <= (256 << 20):
+        need_stage = max(need_stage, m * n * 2 * splits_hint)
+    need_counters = plan["counter_bytes"]
     op = _OPS.get(key)
     if op is not None:
-        stage_bytes, counter_bytes = op.ext.gemm_rs_workspace_bytes(m, n, ws)
-        if stage_bytes <= op.ws.layout.size("stage0") and counter_bytes <= op.ws.layout.size("counters0"):
+        if need_stage <= op.stage_bytes and need_counters <= op.counter_bytes:
             return op
         torch.cuda.synchronize()
         if initialized:
             dist.barrier(group=group)
         op.close()
-        m, n = max(m, op.max_m), max(n, op.max_n)
-    op = GemmRS(m, n, group=group)
+        need_stage, need_counters = max(need_stage, op.stage_bytes), max(need_counters, op.counter_bytes)
+    op = GemmRS(need_stage, need_counters, group=group)
     _OPS[key] = op
     return op
 
@@ -151,5 +185,5 @@ def custom_kernel(data: GemmRsInput, bias_mode: str = "per_rank", backend: str =
             return out + bias
         return gemm_rs_torch(data)
     with torch.cuda.device(a.device):
-        op = get_op(a.shape[0], w.shape[0])
+        op = get_op(a.shape[0], w.shape[0], a.shape[1])
         return op(a, w, bias, bias_mode)

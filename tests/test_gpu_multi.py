@@ -96,7 +96,7 @@ def _gemm_rank(rank, world_size, shapes, repeats):
         torch.cuda.synchronize()
         ok, msg = True, ""
         try:
-            gemm_rs.get_op(m, n).check()
+            gemm_rs.get_op(m, n, k // world_size).check()
         except Exception as exc:  # noqa: BLE001
             ok, msg = False, str(exc)
         a_all, w_all = [e[0] for e in everyone], [e[1] for e in everyone]

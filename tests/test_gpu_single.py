@@ -128,7 +128,7 @@ def test_gemm_world1_matches_fp32_reference(m, n, k, has_bias):
     a, w, bias = contract.make_gemm_rs_inputs(0, 1, m, n, k, has_bias, 5, device="cuda")
     out = gemm_rs.custom_kernel((a, w, bias))
     torch.cuda.synchronize()
-    gemm_rs.get_op(m, n).check()
+    gemm_rs.get_op(m, n, k).check()
     truth = a.float() @ w.float().T
     if has_bias:
         truth = truth + bias.float()
@@ -151,22 +151,27 @@ def test_gemm_world1_reference_inputs_pass_reference_checker(m, n, k, has_bias):
     assert oracle.relative_error(out, truth) < 5e-3
 
 
-@pytest.mark.parametrize("block_n,cta_pair", [(64, 0), (128, 0), (256, 0), (128, 1), (256, 1)])
+@pytest.mark.parametrize("block_n,cta_pair,splits",
+                         [(64, 0, 1), (128, 0, 1), (256, 0, 1), (128, 1, 1), (192, 1, 1), (256, 1, 1),
+                          (256, 1, 3), (192, 1, 2), (128, 0, 4)])
 @pytest.mark.parametrize("m,n,k", [(384, 1024, 832), (128, 256, 64), (1000, 2880, 360), (2048, 2048, 2048)])
-def test_gemm_tile_shapes_single_cta_and_cta_pair(block_n, cta_pair, m, n, k):
+def test_gemm_tile_shapes_single_cta_and_cta_pair(block_n, cta_pair, splits, m, n, k):
     """Every tile width, as single CTAs and as CTA pairs (256-row tiles, odd block counts
     and ragged edges included), gives the same GEMM."""
     from amd_distributed_2025_b200.models import gemm_rs
 
     a, w, bias = contract.make_gemm_rs_inputs(0, 1, m, n, k, True, 9, device="cuda")
-    op = gemm_rs.get_op(m, n)
-    op.block_n, op.cta_pair = block_n, cta_pair
+    if splits > (k + 63) // 64:
+        pytest.skip("more K slices than k-blocks")
+    op = gemm_rs.get_op(m, n, k)
+    op.block_n, op.cta_pair, op.splits = block_n, cta_pair, splits
     try:
-        out = op(a, w, bias)
+        for _ in range(3):  # staged paths alternate parities and reset their counters
+            out = op(a, w, bias)
         torch.cuda.synchronize()
         op.check()
     finally:
-        op.block_n, op.cta_pair = 0, -1
+        op.block_n, op.cta_pair, op.splits = 0, -1, 0
     truth = a.float() @ w.float().T + bias.float()
     assert oracle.relative_error(out, truth) < 5e-3
     want = oracle.gemm_rs_fused_rounding([a], [w], bias, 0)
