@@ -172,6 +172,20 @@ void moe_combine(SymmHeap& heap, at::Tensor out, const at::Tensor& weights, cons
   cuda_check(b200::launch_moe_combine(p, at::cuda::getCurrentCUDAStream()), "moe_combine launch");
 }
 
+// The whole task pipeline in one call: dispatch, the per-rank scale that stands in for the
+// expert computation (all2all/reference.py:262), combine.  Three launches, no host work in
+// between, so short problems are not bound by the Python call overhead.
+void moe_forward(SymmHeap& heap, const at::Tensor& x, const at::Tensor& indices, const at::Tensor& weights,
+                 at::Tensor out, int64_t num_experts, int64_t max_recv, int64_t off_counts, int64_t off_expert_x,
+                 int64_t off_expert_meta, int64_t off_expert_y, at::Tensor expert_x, at::Tensor expert_y,
+                 at::Tensor blk_hist, at::Tensor local_rank, at::Tensor route, at::Tensor expert_num_tokens,
+                 double scale, int64_t dispatch_epoch, int64_t combine_epoch, int64_t timeout_ns) {
+  moe_dispatch(heap, x, indices, num_experts, max_recv, off_counts, off_expert_x, off_expert_meta, blk_hist,
+               local_rank, route, expert_num_tokens, dispatch_epoch, timeout_ns);
+  moe_expert_scale(expert_x, expert_y, expert_num_tokens, scale);
+  moe_combine(heap, out, weights, route, x.size(0), max_recv, off_expert_y, combine_epoch, timeout_ns);
+}
+
 // ------------------------------------------------------------------------- GEMM-RS ----
 
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
@@ -276,6 +290,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_expert_scale", &moe_expert_scale);
   m.def("moe_combine", &moe_combine);
+  m.def("moe_forward", &moe_forward);
   m.def("gemm_rs", &gemm_rs);
   m.def("gemm_rs_plan", [](int64_t M, int64_t N, int64_t K, int64_t ws, int64_t block_n, int64_t cta_pair, int64_t splits) {
     const b200::GemmRsPlan p = b200::gemm_rs_plan((int)M, (int)N, (int)K, (int)ws, (int)block_n, (int)cta_pair, (int)splits);

@@ -54,7 +54,7 @@ struct GemmRsArgs {
 // its arguments (and the SM count), so every rank derives the same plan.
 struct GemmRsPlan {
   int block_n, cta_pair, splits;
-  uint64_t stage_bytes;    // bf16 [world * splits][M / world][N]
+  uint64_t stage_bytes;    // bf16 [world][M / world][N]; fp32 [world * splits][M / world][N] when K is cut
   uint64_t counter_bytes;  // uint32 [m_tiles][n_tiles][4]
 };
 GemmRsPlan gemm_rs_plan(int M, int N, int K, int world_size, int block_n, int cta_pair, int splits);

@@ -4,13 +4,15 @@
 // tcgen05 cta_group::2) per 256 x BN tile, where each CTA loads half of the W tile and the
 // leader's single MMA instruction feeds both tensor-memory halves.  No load is multicast.
 //
-// Warp roles inside one persistent CTA (192 threads, one CTA per SM):
+// Warp roles inside one persistent CTA (224 threads, one CTA per SM):
 //   warp 0        TMA producer: fills a ring of shared-memory stages with A and W tiles
 //   warp 1        MMA issuer: one lane issues tcgen05.mma, accumulating in tensor memory;
 //                 also owns the tensor-memory allocation
 //   warps 2..5    epilogue: tcgen05.ld the accumulator, round to bf16, transpose through
 //                 shared memory so that every warp store covers whole 256-byte row
-//                 segments, store to the owner's staging buffer (peer memory), signal
+//                 segments, store to the owner's staging buffer (peer memory)
+//   warp 6        signaller: after a tile's rows are stored, fences once and bumps the
+//                 owners' arrival counters, keeping that latency off the epilogue warps
 // After its share of GEMM tiles every CTA joins the reduction of this rank's own rows.
 //
 // Every wait (mbarrier or peer counter) is bounded; on expiry the kernel records a status,
@@ -33,7 +35,7 @@ namespace {
 constexpr int BM = kGemmRsBlockM;  // 128: one TMEM lane per output row
 constexpr int BK = kGemmRsBlockK;  // 64 bf16 = one 128-byte swizzled row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // producer, MMA issuer, 4 epilogue warps, signaller
 constexpr int kEpilogueWarps = 4;
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in maximum per CTA
 
@@ -267,6 +269,101 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
   }
 }
 
+// Same for a K-sliced problem, whose staging holds fp32 slices [world * splits][R][N].  The
+// slices of one rank are summed in fp32 and rounded to bf16 -- that is the rank's matmul
+// output in the reference -- the bias is added per rank in bf16 if the reference order was
+// asked for, and the ranks are then summed in fp32 and rounded once.
+__device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const float* stage, int r0, int row_lo,
+                                                    int c0, int vec_per_row, int items, int tid) {
+  constexpr int U = 4;
+  const size_t R = (size_t)p.rows_per_rank;
+  for (int base = tid; base < items; base += kThreads * U) {
+    float acc[U][8];
+    size_t off[U];
+    float bias_f[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * kThreads;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc[u][e] = 0.f;
+        bias_f[u][e] = 0.f;
+      }
+      off[u] = ~(size_t)0;
+      if (i < items) {
+        const int rl = r0 + i / vec_per_row - row_lo;
+        const int n = c0 + ((i % vec_per_row) << 3);
+        off[u] = (size_t)rl * p.N + n;
+        if (p.bias != nullptr) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            bias_f[u][2 * e] = f.x;
+            bias_f[u][2 * e + 1] = f.y;
+          }
+        }
+      }
+    }
+    for (int r = 0; r < p.world_size; ++r) {
+      float part[U][8];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part[u][e] = 0.f;
+      for (int sl = 0; sl < p.splits; ++sl) {
+        const float* src = stage + (size_t)(r * p.splits + sl) * R * p.N;
+        uint4 lo[U], hi[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (off[u] != ~(size_t)0) {
+            lo[u] = __ldcg(reinterpret_cast<const uint4*>(src + off[u]));
+            hi[u] = __ldcg(reinterpret_cast<const uint4*>(src + off[u] + 4));
+          } else {
+            lo[u] = make_uint4(0, 0, 0, 0);
+            hi[u] = make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          part[u][0] += __uint_as_float(lo[u].x);
+          part[u][1] += __uint_as_float(lo[u].y);
+          part[u][2] += __uint_as_float(lo[u].z);
+          part[u][3] += __uint_as_float(lo[u].w);
+          part[u][4] += __uint_as_float(hi[u].x);
+          part[u][5] += __uint_as_float(hi[u].y);
+          part[u][6] += __uint_as_float(hi[u].z);
+          part[u][7] += __uint_as_float(hi[u].w);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float v = __bfloat162float(__float2bfloat16_rn(part[u][e]));
+          if (p.bias_at_source) v = __bfloat162float(__float2bfloat16_rn(v + bias_f[u][e]));
+          acc[u][e] += v;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (off[u] == ~(size_t)0) continue;
+      if (!p.bias_at_source) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u][e] = fmaf(bias_f[u][e], p.bias_scale, acc[u][e]);
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+      o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+      o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+      o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+      *reinterpret_cast<uint4*>(p.out + off[u]) = o;
+    }
+  }
+}
+
 }  // namespace
 
 template <int BN, int CTAS>
@@ -294,6 +391,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (C::kStages + s); };
   auto tfull_bar = [&](uint32_t s) { return bar_base + 8u * (2 * C::kStages + s); };
   auto tempty_bar = [&](uint32_t s) { return bar_base + 8u * (2 * C::kStages + 2 + s); };
+  auto sfull_bar = [&](uint32_t s) { return bar_base + 8u * (2 * C::kStages + 4 + s); };   // tile stored by all 4 warps
+  auto sempty_bar = [&](uint32_t s) { return bar_base + 8u * (2 * C::kStages + 6 + s); };  // signaller took it
 
   if (tid == 0) {
     abort_flag = 0;
@@ -304,6 +403,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(tfull_bar(s), 1);
       ptx::mbar_init(tempty_bar(s), kEpilogueWarps * CTAS);  // every epilogue warp of the pair
+      ptx::mbar_init(sfull_bar(s), kEpilogueWarps);
+      ptx::mbar_init(sempty_bar(s), 1);
     }
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -405,7 +506,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         else ptx::umma_commit(tfull_bar(acc));
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ================================ epilogue =========================================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t slab = smem_epi + (uint32_t)(warp - 2) * C::kSlabBytes;
@@ -413,6 +514,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     constexpr int kRowsPerStore = 32 / kChunksPerRow;    // slab rows covered by one warp store
     constexpr int kRowPitch = C::kEpiCols * 2;
     const bool direct = (p.world_size == 1 && p.splits == 1);
+    const bool sliced = p.splits > 1;
     const int R = p.rows_per_rank;
     const int row_lo = p.rank * R;
     uint32_t* my_counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
@@ -432,19 +534,33 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const bool owned = !direct && tile_owned(p, mb);
       const size_t ctr_index = ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps + q;
       bool peers_ok = true;
+      // One pass fills the warp's slab (32 rows x kEpiCols * 2 bytes): kEpiCols bf16 columns,
+      // or half as many fp32 columns for a K-sliced problem (staged un-rounded).
+      const int cols_per_pass = sliced ? C::kEpiCols / 2 : C::kEpiCols;
+      const int passes = BN / cols_per_pass;
 #pragma unroll 1
-      for (int half = 0; half < BN / C::kEpiCols; ++half) {
-        // ---- TMEM -> registers -> bf16 -> swizzled slab (row = lane) --------------------
+      for (int half = 0; half < passes; ++half) {
+        // ---- TMEM -> registers -> (bf16) -> swizzled slab (row = lane) ------------------
 #pragma unroll 1
-        for (int c = 0; c < C::kEpiCols / 32; ++c) {
+        for (int c = 0; c < cols_per_pass / 32; ++c) {
           uint32_t v[32];
           const uint32_t taddr =
-              tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::kAccStride + half * C::kEpiCols + c * 32;
+              tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::kAccStride + half * cols_per_pass + c * 32;
           ptx::tmem_ld_32x32b_x32(taddr, v);
           ptx::tmem_ld_wait();
-          // with K slices, only slice 0 of a rank carries that rank's bias
-          if (p.bias != nullptr && (direct || (p.bias_at_source && split == 0))) {
-            const int nbase = n0 + half * C::kEpiCols + c * 32;
+          if (sliced) {
+#pragma unroll
+            for (int j8 = 0; j8 < 8; ++j8) {
+              const int chunk = c * 8 + j8;  // 16-byte chunk = 4 fp32 columns
+              const uint32_t addr = slab + lane * kRowPitch + (uint32_t)((chunk ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * j8]), "r"(v[4 * j8 + 1]),
+                           "r"(v[4 * j8 + 2]), "r"(v[4 * j8 + 3])
+                           : "memory");
+            }
+            continue;
+          }
+          if (p.bias != nullptr && (direct || p.bias_at_source)) {
+            const int nbase = n0 + half * cols_per_pass + c * 32;
             if (p.bias_at_source) {
               // reference order: round the product to bf16, add the bf16 bias, round again
 #pragma unroll
@@ -476,7 +592,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                          : "memory");
           }
         }
-        if (half == BN / C::kEpiCols - 1) {
+        if (half == passes - 1) {
           // all TMEM reads of this accumulator are done: hand it back to the MMA warp
           ptx::tcgen05_fence_before();
           __syncwarp();
@@ -512,9 +628,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                        : "r"(addr)
                        : "memory");
           const int m = m0 + rr;
-          const int n = n0 + half * C::kEpiCols + cc * 8;
+          const int n = n0 + half * cols_per_pass + cc * (sliced ? 4 : 8);
           if (m < p.M && n < p.N) {
-            if (direct) {
+            if (sliced) {
+              const int owner = m / R;
+              const int rl = m - owner * R;
+              float* dst = peer_ptr<float>(p.peer_base[owner], p.off_stage) +
+                           ((size_t)(p.rank * p.splits + split) * R + rl) * p.N + n;
+              *reinterpret_cast<uint4*>(dst) = val;
+            } else if (direct) {
               *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = val;
             } else if (owned) {
               if (peers_ok) {
@@ -535,26 +657,51 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
       if (owned) {
         if (lane == 0) my_counters[ctr_index] = 0;  // next used by the call after next
-      } else if (!direct) {
-        // Tell every owner with rows in this tile that warp q's 32 rows have been stored.
-        // Device scope is enough (and much cheaper) when the only owner is this GPU.
-        __syncwarp();
-        if (lane == 0) {
+      }
+      // Hand the stored tile to the signaller warp: it pays for the fence that must precede
+      // the arrival counters, so this warp can start on the next accumulator right away.
+      __syncwarp();
+      if (!direct && lane == 0) {
+        if (mbar_wait(sempty_bar(acc), acc_phase ^ 1u, &abort_flag, limit, p.status, 500 + (int)acc))
+          ptx::mbar_arrive(sfull_bar(acc));
+      }
+      // reconverge: the next tile starts with warp-wide (.sync.aligned) tensor-memory loads
+      __syncwarp();
+    }
+  } else if (warp == 6) {
+    // ================================ signaller ========================================
+    // For every staged tile: once all four epilogue warps have stored their rows, make the
+    // stores visible (one fence for the whole CTA's tile) and bump the owners' counters.
+    if (lane == 0 && !(p.world_size == 1 && p.splits == 1)) {
+      const int R = p.rows_per_rank;
+      uint32_t it = 0;
+      for (int t = gidx; t < total_tiles && !abort_flag; t += GG, ++it) {
+        int mb, nb, split;
+        tile_coords<CTAS>(p, t, cta_rank, mb, nb, split);
+        const uint32_t acc = it & 1u;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(sfull_bar(acc), acc_phase, &abort_flag, limit, p.status, 600 + (int)acc)) break;
+        if (!tile_owned(p, mb)) {
           const int m_lo = mb * BM;
           const int m_hi = min(p.M, m_lo + BM) - 1;
           const int o_lo = m_lo / R;
           const int o_hi = m_hi / R;
           if (o_lo <= o_hi) {
-            const bool local_only = (o_lo == p.rank && o_hi == p.rank);
-            if (local_only) __threadfence();
+            // device scope is enough (and much cheaper) when the only owner is this GPU
+            if (o_lo == p.rank && o_hi == p.rank) __threadfence();
             else __threadfence_system();
+            const size_t base_index = ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps;
             for (int o = o_lo; o <= o_hi; ++o) {
-              uint32_t* ctr = peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + ctr_index;
-              if (o == p.rank) red_release_gpu_add(ctr, 1u);
-              else red_release_sys_add(ctr, 1u);
+              uint32_t* ctr = peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + base_index;
+#pragma unroll
+              for (int w = 0; w < kEpilogueWarps; ++w) {
+                if (o == p.rank) red_release_gpu_add(ctr + w, 1u);
+                else red_release_sys_add(ctr + w, 1u);
+              }
             }
           }
         }
+        ptx::mbar_arrive(sempty_bar(acc));
       }
     }
   }
@@ -617,7 +764,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const int c0 = nb * BN;
         const int c1 = min(c0 + BN, p.N);
         const int vec_per_row = (c1 - c0) >> 3;
-        reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
+        if (p.splits > 1) {
+          reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
+                              (r1 - r0) * vec_per_row, tid);
+        } else {
+          reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
+        }
       }
       __syncthreads();
       if (tid < kEpilogueWarps) ctr[tid] = 0;  // this parity's counters are next used two calls from now
@@ -703,7 +855,9 @@ GemmRsPlan make_plan(int M, int N, int K, int world_size, int sms, int force_bn,
     best.cta_pair = 0;
     best.splits = 1;
   }
-  best.stage_bytes = (uint64_t)best.splits * (uint64_t)M * (uint64_t)N * 2ull;
+  // bf16 partials per rank, or fp32 slices when K is cut
+  best.stage_bytes = best.splits > 1 ? (uint64_t)best.splits * (uint64_t)M * (uint64_t)N * 4ull
+                                     : (uint64_t)M * (uint64_t)N * 2ull;
   const uint64_t n_tiles = (N + 63) / 64;
   best.counter_bytes = ((uint64_t)m_tiles * n_tiles * kEpilogueWarps * 4 + 255) / 256 * 256;
   (void)world_size;

@@ -87,6 +87,10 @@ class MoEAllToAll:
         self._route = torch.full((n_max, 2), -1, **i32)
         self.expert_num_tokens = torch.zeros(self.num_local_experts, **i32)
         self._num_tokens = 0
+        self._off_counts = self.ws.offset("counts")
+        self._off_expert_x = self.ws.offset("expert_x")
+        self._off_expert_meta = self.ws.offset("expert_meta")
+        self._off_expert_y = self.ws.offset("expert_y")
 
     # -- dispatch ----------------------------------------------------------------------
     def dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -174,6 +178,29 @@ class MoEAllToAll:
                 out_tokens[:n] = target[:n].to(out_tokens.dtype)
         return out_tokens
 
+    # -- the task pipeline in one native call -------------------------------------------
+    def forward(self, dp_x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, scale: float) -> torch.Tensor:
+        """dispatch -> ``expert_y = expert_x * scale`` -> combine, launched back to back from
+        one native call (same kernels and protocol as the three separate methods)."""
+        cfg = self.cfg
+        if dp_x.shape[0] > cfg.max_num_tokens or dp_x.shape[1] != cfg.hidden_dim or dp_x.dtype != cfg.in_dtype:
+            raise ValueError("dp_x does not match the configuration")
+        if indices.shape[1] != cfg.experts_per_token:
+            raise ValueError("indices do not match the configuration")
+        self.ws.check()
+        x = dp_x if dp_x.is_contiguous() else dp_x.contiguous()
+        idx = indices if (indices.dtype == torch.int32 and indices.is_contiguous()) else indices.to(torch.int32).contiguous()
+        w = weights if (weights.dtype == torch.float32 and weights.is_contiguous()) else weights.to(torch.float32).contiguous()
+        self._num_tokens = x.shape[0]
+        out = torch.empty((x.shape[0], cfg.hidden_dim), dtype=cfg.out_dtype, device=x.device)
+        self.ext.moe_forward(
+            self.ws.heap, x, idx, w, out, cfg.num_experts, self.max_recv,
+            self._off_counts, self._off_expert_x, self._off_expert_meta, self._off_expert_y,
+            self.expert_x, self.expert_y, self._blk_hist, self._local_rank, self._route, self.expert_num_tokens,
+            float(scale), self.ws.next_epoch("moe_dispatch"), self.ws.next_epoch("moe_combine"), self.ws.wait_limit_ns,
+        )
+        return out
+
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
 
@@ -230,10 +257,5 @@ def custom_kernel(data: MoEInput, backend: str = "auto") -> torch.Tensor:
         y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=x.device)
         ata.combine(y, rank_data.weights, em, ey, n_tok)
         return y[: rank_data.num_tokens]
-    with torch.cuda.device(x.device):
-        layer = get_layer(cfg, rank, world_size)
-        n_tok, ex, em = layer.dispatch(x, rank_data.indices)
-        ey = layer.expert_scale(1 + rank)
-        y = torch.empty(rank_data.num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=x.device)
-        layer.combine(y, rank_data.weights, em, ey, n_tok, rank_data.num_tokens)
-    return y
+    layer = get_layer(cfg, rank, world_size)
+    return layer.forward(x, rank_data.indices, rank_data.weights, 1 + rank)
