@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "fp8_gemm.h"
 #include "gemm_rs.h"
 #include "moe.h"
 #include "status.h"
@@ -191,7 +192,7 @@ void moe_forward(SymmHeap& heap, const at::Tensor& x, const at::Tensor& indices,
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
              at::Tensor out, double bias_scale, bool bias_at_source, int64_t off_stage, int64_t off_counters, int64_t epoch,
              int64_t timeout_ns, int64_t max_ctas, int64_t block_n, int64_t cta_pair, int64_t splits,
-             const c10::optional<at::Tensor>& trace) {
+             const c10::optional<at::Tensor>& trace, int64_t debug, bool fuse_own, bool tma_store, bool force_staged) {
   TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
               "input and weight must be bf16 CUDA tensors");
@@ -233,12 +234,52 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.cta_pair = (int)cta_pair;
   g.splits = (int)splits;
   g.trace = nullptr;
+  g.debug = (int)debug;
+  g.fuse_own = fuse_own ? 1 : 0;
+  g.tma_store = tma_store ? 1 : 0;
+  g.force_staged = force_staged ? 1 : 0;
   if (trace.has_value() && trace->defined()) {
-    TORCH_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 4 * 160,
-                "trace must be a contiguous int64 tensor with at least 640 elements");
+    TORCH_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 8 * 160,
+                "trace must be a contiguous int64 tensor with at least 1280 elements");
     g.trace = reinterpret_cast<uint64_t*>(trace->data_ptr<int64_t>());
   }
   cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
+}
+
+// ------------------------------------------------------------------------ fp8 GEMM ----
+
+void fp8_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& a_scale, const at::Tensor& b_scale,
+              at::Tensor c, at::Tensor error_flag, int64_t timeout_ns) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1),
+              "a [M, K] and b [N, K] must be CUDA matrices with equal K");
+  TORCH_CHECK(a.scalar_type() == at::kFloat8_e4m3fn && b.scalar_type() == at::kFloat8_e4m3fn, "a and b must be float8_e4m3fn");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous(), "a and b must be row-major (K contiguous)");
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+  const int64_t kb = (K + 127) / 128, nb = (N + 127) / 128;
+  TORCH_CHECK(a_scale.scalar_type() == at::kFloat && a_scale.dim() == 2 && a_scale.size(0) == M && a_scale.size(1) == kb,
+              "a_scale must be fp32 [M, ceil(K/128)]");
+  TORCH_CHECK(b_scale.scalar_type() == at::kFloat && b_scale.dim() == 2 && b_scale.size(0) == nb && b_scale.size(1) == kb,
+              "b_scale must be fp32 [ceil(N/128), ceil(K/128)]");
+  TORCH_CHECK(c.scalar_type() == at::kBFloat16 && c.is_contiguous() && c.size(0) == M && c.size(1) == N, "c must be bf16 [M, N]");
+  TORCH_CHECK(K % 16 == 0, "K must be a multiple of 16");
+  TORCH_CHECK(error_flag.scalar_type() == at::kInt && error_flag.numel() >= 1, "error_flag must be an int32 tensor");
+  c10::cuda::CUDAGuard guard(a.device());
+  b200::Fp8GemmArgs g;
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.a_scale = a_scale.data_ptr<float>();
+  g.b_scale = b_scale.data_ptr<float>();
+  g.c = c.data_ptr();
+  g.M = (int)M;
+  g.N = (int)N;
+  g.K = (int)K;
+  g.as_stride_m = a_scale.stride(0);
+  g.as_stride_k = a_scale.stride(1);
+  g.bs_stride_n = b_scale.stride(0);
+  g.bs_stride_k = b_scale.stride(1);
+  g.timeout_ns = (uint64_t)timeout_ns;
+  g.error_flag = error_flag.data_ptr<int32_t>();
+  cuda_check(b200::launch_fp8_gemm(g, at::cuda::getCurrentCUDAStream()), "fp8_gemm launch");
 }
 
 }  // namespace
@@ -271,6 +312,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("peer_base", [](const SymmHeap& h, int r) { return (int64_t)h.peer_base(r); })
       .def("view", &heap_view, py::arg("offset"), py::arg("shape"), py::arg("dtype"))
       .def("status", [](const SymmHeap& h) { return status_to_dict(h.status_host()); })
+      .def("status_code", [](const SymmHeap& h) { return (int)h.status_host().code; })
       .def("status_sync", [](const SymmHeap& h) { return status_to_dict(h.status_sync()); })
       .def("reset_status", &SymmHeap::reset_status)
       .def("barrier",
@@ -292,6 +334,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_combine", &moe_combine);
   m.def("moe_forward", &moe_forward);
   m.def("gemm_rs", &gemm_rs);
+  m.def("fp8_gemm", &fp8_gemm);
   m.def("gemm_rs_plan", [](int64_t M, int64_t N, int64_t K, int64_t ws, int64_t block_n, int64_t cta_pair, int64_t splits) {
     const b200::GemmRsPlan p = b200::gemm_rs_plan((int)M, (int)N, (int)K, (int)ws, (int)block_n, (int)cta_pair, (int)splits);
     py::dict d;

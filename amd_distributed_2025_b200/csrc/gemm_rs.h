@@ -46,8 +46,14 @@ struct GemmRsArgs {
   int block_n;   // 0 = choose from the shape; else 64, 128 or 256
   int cta_pair;  // -1 = choose from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
   int splits;    // 0 = choose from the shape; else the number of K slices per tile
-  uint64_t* trace;  // optional device buffer [CTAs][4] of globaltimer stamps (start, pipeline ready,
-                    // GEMM tiles done, exit); nullptr = no tracing
+  uint64_t* trace;  // optional device buffer [CTAs][8] of globaltimer stamps (start, pipeline ready, GEMM
+                    // tiles done, exit, first own tile reached, its peers' rows arrived, last own tile
+                    // stored); nullptr = no tracing
+  int debug;        // measurement aids, results are wrong when set: 1 = stage locally, 2 = do not stage
+  int fuse_own;     // 1 = a rank adds the peers' rows to its own tiles in their epilogue; 0 = own tiles are
+                    // staged like the others and reduced by all CTAs after the GEMM tiles
+  int tma_store;    // 0 = per-lane staging stores only; otherwise TMA stores where the shape allows
+  int force_staged; // 1 = stage and reduce even on a single rank (exercises the staged path on one GPU)
 };
 
 // How a problem will be run, and what ONE parity of its workspace needs.  A pure function of

@@ -23,6 +23,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <cstring>
 
 #include "gemm_rs.h"
 #include "signal.cuh"
@@ -50,8 +51,10 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTxBytes = CTAS * kStageBytes;   // bytes counted on the (leader's) full barrier
   static constexpr int kEpiCols = (BN % 128 == 0) ? 128 : 64;  // columns transposed at a time
-  static constexpr int kSlabBytes = 32 * kEpiCols * 2;  // per epilogue warp
-  static constexpr int kEpiBytes = kEpilogueWarps * kSlabBytes;
+  static constexpr int kSlabBytes = 32 * kEpiCols * 2;  // one transpose buffer of an epilogue warp:
+                                                        // kEpiCols / 64 sub-slabs of 32 rows x 128 bytes
+  static constexpr int kSlabBuffers = 2;                // filled alternately; TMA drains one while the other fills
+  static constexpr int kEpiBytes = kEpilogueWarps * kSlabBuffers * kSlabBytes;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kStagesRaw = (kSmemLimit - 1024 - kEpiBytes - kBarrierBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -84,11 +87,30 @@ struct KernelParams {
   uint64_t off_stage, off_counters;
   uint64_t epoch, timeout_ns;
   StatusBlock* status;
-  uint64_t* trace;  // optional [gridDim.x][4] globaltimer stamps: start, pipeline ready, GEMM tiles done, exit
+  uint64_t* trace;  // optional [gridDim.x][8] globaltimer stamps: 0 start, 1 pipeline ready, 2 GEMM tiles done,
+                    // 3 exit, 4 first own tile reached, 5 its peers' rows arrived, 6 last own tile stored
+  int debug;        // measurement aids (results are wrong when set): 1 = stage into this GPU's own memory
+                    // instead of the owner's, 2 = skip the staging stores
+  int fuse_own;     // 1: a rank finishes its own tiles in their epilogue (adds the peers' rows there);
+                    // 0: it stages them like everybody else and all CTAs reduce after the GEMM tiles
+  int direct;       // 1: one rank, K not sliced: tiles are written straight to `out`, nothing is staged
+  int tma_store;    // 1: whole 32-row groups go to one owner and there are tensor maps for every owner:
+                    // staged tiles leave through TMA stores instead of per-lane stores
+};
+
+constexpr int kMaxStageMaps = 8;
+struct StageMaps {
+  CUtensorMap m[kMaxStageMaps];  // m[o]: rank o's staging block for partials coming from this rank, bf16 [R, N]
 };
 
 __device__ __forceinline__ void trace_stamp(const KernelParams& p, int slot) {
-  if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * 4 + slot] = global_timer_ns();
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
+}
+__device__ __forceinline__ void trace_stamp_any(const KernelParams& p, int slot, bool first_only) {
+  if (p.trace == nullptr) return;
+  uint64_t* w = p.trace + (size_t)blockIdx.x * 8 + slot;
+  if (first_only && *w != 0) return;
+  *w = global_timer_ns();
 }
 
 struct PipeState {
@@ -149,7 +171,7 @@ __device__ __forceinline__ void tile_coords(const KernelParams& p, int t, uint32
 __device__ __forceinline__ bool tile_owned(const KernelParams& p, int mb) {
   const int lo = mb * BM;
   const int row_lo = p.rank * p.rows_per_rank;
-  return p.splits == 1 && lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
+  return p.fuse_own && p.splits == 1 && lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
 }
 
 // Sum of the world_size bf16 partial vectors of out[rl, n..n+8) in rank order, in fp32,
@@ -369,7 +391,7 @@ __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const
 template <int BN, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const KernelParams p) {
+               const __grid_constant__ StageMaps stage_maps, const KernelParams p) {
   using C = Cfg<BN, CTAS>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_flag;
@@ -509,11 +531,17 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else if (warp < 6) {
     // ================================ epilogue =========================================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const uint32_t slab = smem_epi + (uint32_t)(warp - 2) * C::kSlabBytes;
-    constexpr int kChunksPerRow = C::kEpiCols / 8;       // 16-byte chunks per slab row
-    constexpr int kRowsPerStore = 32 / kChunksPerRow;    // slab rows covered by one warp store
-    constexpr int kRowPitch = C::kEpiCols * 2;
-    const bool direct = (p.world_size == 1 && p.splits == 1);
+    const uint32_t slab0 = smem_epi + (uint32_t)(warp - 2) * (C::kSlabBuffers * C::kSlabBytes);
+    constexpr int kChunksPerRow = C::kEpiCols / 8;       // 16-byte chunks per tile row held in a buffer
+    constexpr int kRowsPerStore = 32 / kChunksPerRow;    // rows covered by one warp store
+    constexpr int kSubBytes = 32 * 128;                  // one sub-slab: 32 rows x 128 bytes, 128B-swizzled
+    // 16-byte chunk `chunk` of row `row`: sub-slab chunk / 8, position (chunk % 8) ^ (row % 8).
+    // This is the layout a 128-byte-swizzled TMA box {64 bf16, 32 rows} expects.
+    auto slab_addr = [&](uint32_t buf, int row, int chunk) {
+      return buf + (uint32_t)(chunk >> 3) * kSubBytes + (uint32_t)row * 128u + (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
+    };
+    uint32_t pass_count = 0;
+    const bool direct = p.direct != 0;
     const bool sliced = p.splits > 1;
     const int R = p.rows_per_rank;
     const int row_lo = p.rank * R;
@@ -538,8 +566,16 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       // or half as many fp32 columns for a K-sliced problem (staged un-rounded).
       const int cols_per_pass = sliced ? C::kEpiCols / 2 : C::kEpiCols;
       const int passes = BN / cols_per_pass;
+      // Whole 32-row groups of a staged tile leave through TMA stores (asynchronous, so NVLink
+      // back-pressure never blocks this warp); everything else takes the per-lane store loop.
+      const bool tma_tile = p.tma_store && !direct && !owned && !sliced && m0 < p.M;
+      const int owner0 = tma_tile ? m0 / R : 0;
 #pragma unroll 1
-      for (int half = 0; half < passes; ++half) {
+      for (int half = 0; half < passes; ++half, ++pass_count) {
+        const uint32_t slab = slab0 + (pass_count & 1u) * C::kSlabBytes;
+        // the TMA store that last read this buffer (two passes ago) must be done with it
+        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
         // ---- TMEM -> registers -> (bf16) -> swizzled slab (row = lane) ------------------
 #pragma unroll 1
         for (int c = 0; c < cols_per_pass / 32; ++c) {
@@ -552,7 +588,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
             for (int j8 = 0; j8 < 8; ++j8) {
               const int chunk = c * 8 + j8;  // 16-byte chunk = 4 fp32 columns
-              const uint32_t addr = slab + lane * kRowPitch + (uint32_t)((chunk ^ (lane & 7)) << 4);
+              const uint32_t addr = slab_addr(slab, lane, chunk);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * j8]), "r"(v[4 * j8 + 1]),
                            "r"(v[4 * j8 + 2]), "r"(v[4 * j8 + 3])
                            : "memory");
@@ -586,7 +622,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             pk.z = pack_bf16x2(__uint_as_float(v[8 * j4 + 4]), __uint_as_float(v[8 * j4 + 5]));
             pk.w = pack_bf16x2(__uint_as_float(v[8 * j4 + 6]), __uint_as_float(v[8 * j4 + 7]));
             const int chunk = c * 4 + j4;
-            const uint32_t addr = slab + lane * kRowPitch + (uint32_t)((chunk ^ (lane & 7)) << 4);
+            const uint32_t addr = slab_addr(slab, lane, chunk);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z),
                          "r"(pk.w)
                          : "memory");
@@ -606,22 +642,40 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           // Rows q*32..q*32+31 of this tile were stored by warp q of every peer; wait for
           // their world_size - 1 arrivals on this warp's counter.
           int ok = 1;
+          if (warp == 2 && lane == 0) trace_stamp_any(p, 4, true);
           if (lane == 0) {
             ok = wait_u32_ge(my_counters + ctr_index, (uint32_t)(p.world_size - 1), limit, p.status, PHASE_RS_PARTIALS,
                              -1, (int)(mb * p.n_tiles + nb), true)
                      ? 1
                      : 0;
           }
+          if (warp == 2 && lane == 0) trace_stamp_any(p, 5, true);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           peers_ok = ok != 0;
           if (!peers_ok) abort_flag = 1;
+        }
+        if (tma_tile) {
+          // ---- slab -> owner's staging block, one TMA box per 64 columns -------------------
+          ptx::fence_proxy_async_smem();  // this lane's slab writes, for the async proxy
+          __syncwarp();
+          if (lane == 0 && p.debug != 2) {
+            const void* map = &stage_maps.m[p.debug == 1 ? p.rank : owner0];
+#pragma unroll
+            for (int sub = 0; sub < C::kEpiCols / 64; ++sub) {
+              const int x = n0 + half * cols_per_pass + sub * 64;
+              if (x < p.N) ptx::tma_store_2d(map, slab + sub * kSubBytes, x, m0 - owner0 * R);
+            }
+            ptx::bulk_commit_group();
+          }
+          __syncwarp();
+          continue;
         }
         // ---- slab -> global, whole row segments per store ------------------------------
 #pragma unroll 2
         for (int s = 0; s < kChunksPerRow; ++s) {
           const int rr = s * kRowsPerStore + lane / kChunksPerRow;
           const int cc = lane % kChunksPerRow;
-          const uint32_t addr = slab + rr * kRowPitch + (uint32_t)((cc ^ (rr & 7)) << 4);
+          const uint32_t addr = slab_addr(slab, rr, cc);
           uint4 val;
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
@@ -644,10 +698,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                 *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) =
                     reduce_partials(p, my_stage, rl, n, &val);
               }
-            } else {
+            } else if (p.debug != 2) {
               const int owner = m / R;
               const int rl = m - owner * R;
-              __nv_bfloat16* dst = peer_ptr<__nv_bfloat16>(p.peer_base[owner], p.off_stage) +
+              __nv_bfloat16* dst = peer_ptr<__nv_bfloat16>(p.peer_base[p.debug == 1 ? p.rank : owner], p.off_stage) +
                                    ((size_t)(p.rank * p.splits + split) * R + rl) * p.N + n;
               *reinterpret_cast<uint4*>(dst) = val;
             }
@@ -657,9 +711,14 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
       if (owned) {
         if (lane == 0) my_counters[ctr_index] = 0;  // next used by the call after next
+        if (warp == 2 && lane == 0) trace_stamp_any(p, 6, false);
       }
       // Hand the stored tile to the signaller warp: it pays for the fence that must precede
       // the arrival counters, so this warp can start on the next accumulator right away.
+      if (tma_tile && lane == 0) {
+        ptx::bulk_wait_group<0>();  // the tile's TMA stores have been performed
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // order them before the generic-proxy signal
+      }
       __syncwarp();
       if (!direct && lane == 0) {
         if (mbar_wait(sempty_bar(acc), acc_phase ^ 1u, &abort_flag, limit, p.status, 500 + (int)acc))
@@ -672,7 +731,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // ================================ signaller ========================================
     // For every staged tile: once all four epilogue warps have stored their rows, make the
     // stores visible (one fence for the whole CTA's tile) and bump the owners' counters.
-    if (lane == 0 && !(p.world_size == 1 && p.splits == 1)) {
+    if (lane == 0 && !p.direct) {
       const int R = p.rows_per_rank;
       uint32_t it = 0;
       for (int t = gidx; t < total_tiles && !abort_flag; t += GG, ++it) {
@@ -724,7 +783,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
   trace_stamp(p, 2);
-  if ((p.world_size == 1 && p.splits == 1) || abort_flag) {
+  if (p.direct || abort_flag) {
     trace_stamp(p, 3);
     return;
   }
@@ -803,8 +862,26 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // Row-major bf16 [rows, cols] tensor, box = [box_rows, 64 columns], 128-byte swizzle,
-// out-of-range elements read as zero.
+// out-of-range elements read as zero.  Encoded maps are kept in a small per-thread cache:
+// a serving loop calls with the same weight (and often the same activation buffer) again
+// and again, and the driver call is a visible part of a short launch.
 bool make_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  struct Entry {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 64;
+  thread_local Entry cache[kEntries];
+  thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i) {
+    const Entry& e = cache[i];
+    if (e.base == base && e.rows == rows && e.cols == cols && e.box_rows == box_rows) {
+      *map = e.map;
+      return true;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -814,7 +891,16 @@ bool make_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  Entry& slot = cache[next];
+  slot.base = base;
+  slot.rows = rows;
+  slot.cols = cols;
+  slot.box_rows = box_rows;
+  slot.map = *map;
+  next = (next + 1) % kEntries;
+  if (used < kEntries) ++used;
+  return true;
 }
 
 // Tile shape and K slicing from the problem size.  Cost model: waves of work items times
@@ -901,6 +987,20 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, int splits, cudaStream_t 
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
   p.trace = a.trace;
+  p.debug = a.debug;
+  p.fuse_own = a.fuse_own;
+  p.direct = (a.world_size == 1 && splits == 1 && !a.force_staged) ? 1 : 0;
+  StageMaps maps;
+  std::memset(&maps, 0, sizeof(maps));
+  p.tma_store = 0;
+  if (a.world_size <= kMaxStageMaps && splits == 1 && !p.direct && p.rows_per_rank % 32 == 0 && a.tma_store != 0) {
+    p.tma_store = 1;
+    for (int o = 0; o < a.world_size; ++o) {
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.peer_base[o]) + a.off_stage +
+                            (uint64_t)a.rank * p.rows_per_rank * a.N * 2ull;
+      if (!make_tensor_map(&maps.m[o], base, (uint64_t)p.rows_per_rank, (uint64_t)a.N, 32)) return cudaErrorInvalidValue;
+    }
+  }
 
   auto kernel = gemm_rs_kernel<BN, CTAS>;
   // Per kernel variant and device, once: opt in to the large dynamic shared memory and ask
@@ -942,7 +1042,7 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, int splits, cudaStream_t 
   if (a.max_ctas > 0) schedulers = std::min(schedulers, std::max(a.max_ctas / CTAS, 1));
   if (schedulers < 1) schedulers = 1;
   cfg.gridDim = dim3((unsigned)(schedulers * CTAS));
-  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
+  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, maps, p);
 }
 
 }  // namespace

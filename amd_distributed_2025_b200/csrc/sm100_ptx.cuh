@@ -50,6 +50,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tenso
       ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Tiled 2-D store, shared -> global (the destination may be a peer GPU's memory), tracked by
+// the issuing thread's bulk async-groups.
+__device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups are still READING their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Wait until at most N of this thread's bulk groups are incomplete (their writes not yet performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }

@@ -70,14 +70,25 @@ class GemmRS:
             device=self.device,
             wait_limit_ms=wait_limit_ms,
         )
+        self._plans: Dict[tuple, dict] = {}
+        self._fits = set()  # problem sizes already known to fit this workspace
         self.max_ctas = 0  # 0 = one CTA per SM
         self.block_n = 0  # 0 = tile width chosen from the shape (64 / 128 / 192 / 256)
         self.cta_pair = -1  # -1 = chosen from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
         self.splits = 0  # 0 = chosen from the shape; else K slices per tile
-        self.trace: Optional[torch.Tensor] = None  # int64 [>=160, 4]: per-CTA globaltimer stamps when set
+        self.trace: Optional[torch.Tensor] = None  # int64 [160, 8]: per-CTA globaltimer stamps when set
+        self.debug = 0  # measurement aids that make results wrong: 1 = stage locally, 2 = do not stage
+        self.fuse_own = False  # True: own tiles add the peers' rows in their epilogue instead of being staged
+        self.tma_store = True  # staged tiles leave through TMA stores where the shape allows
+        self.force_staged = False  # stage and reduce even on one rank (tests the staged path on one GPU)
 
     def plan(self, m: int, n: int, k: int) -> dict:
-        return self.ext.gemm_rs_plan(m, n, k, self.world_size, self.block_n, self.cta_pair, self.splits)
+        key = (m, n, k, self.block_n, self.cta_pair, self.splits)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self.ext.gemm_rs_plan(m, n, k, self.world_size, self.block_n, self.cta_pair, self.splits)
+            self._plans[key] = plan
+        return plan
 
     def fits(self, plan: dict) -> bool:
         return plan["stage_bytes"] <= self.stage_bytes and plan["counter_bytes"] <= self.counter_bytes
@@ -121,13 +132,18 @@ class GemmRS:
             plan["cta_pair"],
             plan["splits"],
             self.trace,
+            self.debug,
+            self.fuse_own,
+            self.tma_store,
+            self.force_staged,
         )
         return out
 
     def enable_trace(self, on: bool = True) -> None:
-        """Record per-CTA phase time stamps (ns) of the next calls into ``self.trace``:
-        columns = kernel start, pipeline ready, GEMM tiles done, exit."""
-        self.trace = torch.zeros((160, 4), dtype=torch.int64, device=self.device) if on else None
+        """Record per-CTA phase time stamps (ns) of the next calls into ``self.trace``: columns =
+        kernel start, pipeline ready, GEMM tiles done, exit, first own tile reached, its
+        peers' rows arrived, last own tile stored."""
+        self.trace = torch.zeros((160, 8), dtype=torch.int64, device=self.device) if on else None
 
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
@@ -151,14 +167,17 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
     initialized = dist.is_available() and dist.is_initialized()
     ws = dist.get_world_size(group) if initialized else 1
     key = (ws, id(group), torch.cuda.current_device())
+    op = _OPS.get(key)
+    if op is not None and (m, n, k) in op._fits:
+        return op
     plan = ext.gemm_rs_plan(m, n, max(k, 64), ws, 0, -1, 0)
     need_stage = plan["stage_bytes"]
     if m * n * 2 * splits_hint <= (256 << 20):
         need_stage = max(need_stage, m * n * 2 * splits_hint)
     need_counters = plan["counter_bytes"]
-    op = _OPS.get(key)
     if op is not None:
         if need_stage <= op.stage_bytes and need_counters <= op.counter_bytes:
+            op._fits.add((m, n, k))
             return op
         torch.cuda.synchronize()
         if initialized:
@@ -184,6 +203,5 @@ def custom_kernel(data: GemmRsInput, bias_mode: str = "per_rank", backend: str =
             out = gemm_rs_torch((a, w, None))
             return out + bias
         return gemm_rs_torch(data)
-    with torch.cuda.device(a.device):
-        op = get_op(a.shape[0], w.shape[0], a.shape[1])
-        return op(a, w, bias, bias_mode)
+    op = get_op(a.shape[0], w.shape[0], a.shape[1])
+    return op(a, w, bias, bias_mode)

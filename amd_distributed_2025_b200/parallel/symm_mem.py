@@ -143,6 +143,8 @@ class SymmetricWorkspace:
 
     def check(self, sync: bool = False) -> None:
         """Raise ``StatusError`` if a kernel recorded a failure (expired wait, bad index)."""
+        if not sync and self.heap.status_code() == 0:
+            return
         st = self.status(sync)
         if st["code"] != 0:
             raise StatusError(describe_status(st, self.rank), st)

@@ -176,3 +176,47 @@ def test_gemm_tile_shapes_single_cta_and_cta_pair(block_n, cta_pair, splits, m, 
     assert oracle.relative_error(out, truth) < 5e-3
     want = oracle.gemm_rs_fused_rounding([a], [w], bias, 0)
     assert oracle.outlier_fraction(out, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL) < 1e-4
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1000, 2944, 1024), (4096, 4096, 2048)])
+def test_fp8_block_scaled_gemm_matches_fp32_reference(m, n, k):
+    from amd_distributed_2025_b200.ops.fp8_gemm import fp8_gemm, fp8_gemm_reference
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    kb, nb = (k + 127) // 128, (n + 127) // 128
+    # scales stored the way the stand-alone template indexes them: [kb][m] and [kb][nb], viewed transposed
+    a_scale = (torch.rand(kb, m, device="cuda", generator=g) + 0.5).t()
+    b_scale = (torch.rand(kb, nb, device="cuda", generator=g) + 0.5).t()
+    c = fp8_gemm(a, b, a_scale, b_scale)
+    torch.cuda.synchronize()
+    want = fp8_gemm_reference(a, b, a_scale, b_scale)
+    assert oracle.relative_error(c, want) < 5e-3
+    assert torch.allclose(c.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+
+
+@pytest.mark.parametrize("tma_store", [True, False])
+@pytest.mark.parametrize("fuse_own", [True, False])
+@pytest.mark.parametrize("m,n,k,block_n,cta_pair", [(2048, 2048, 1024, 256, 1), (1024, 2880, 512, 192, 1), (512, 1024, 256, 128, 0),
+                                                   (1056, 1000, 320, 256, 1)])
+def test_gemm_staged_path_on_one_gpu(tma_store, fuse_own, m, n, k, block_n, cta_pair):
+    """The multi-rank machinery (staging buffer, TMA stores, signaller, arrival counters,
+    reduction) run on a single rank, where its result must equal the plain GEMM."""
+    from amd_distributed_2025_b200.models import gemm_rs
+
+    a, w, bias = contract.make_gemm_rs_inputs(0, 1, m, n, k, True, 13, device="cuda")
+    op = gemm_rs.get_op(m, n, k)
+    op.block_n, op.cta_pair, op.splits = block_n, cta_pair, 1
+    op.force_staged, op.tma_store, op.fuse_own = True, tma_store, fuse_own
+    try:
+        for _ in range(3):
+            out = op(a, w, bias)
+        torch.cuda.synchronize()
+        op.check()
+    finally:
+        op.block_n, op.cta_pair, op.splits = 0, -1, 0
+        op.force_staged, op.tma_store, op.fuse_own = False, True, False
+    want = oracle.gemm_rs_fused_rounding([a], [w], bias, 0)
+    assert oracle.outlier_fraction(out, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL) < 1e-4
+    assert oracle.relative_error(out, a.float() @ w.float().T + bias.float()) < 5e-3
