@@ -174,55 +174,64 @@ __device__ __forceinline__ bool tile_owned(const KernelParams& p, int mb) {
   return p.fuse_own && p.splits == 1 && lo >= row_lo && lo + BM <= row_lo + p.rows_per_rank && lo + BM <= p.M;
 }
 
-// Sum of the world_size bf16 partial vectors of out[rl, n..n+8) in rank order, in fp32,
-// plus the bias, rounded once.  `own` (if given) is this rank's partial, taken from
-// registers instead of the staging buffer.
-__device__ __forceinline__ uint4 reduce_partials(const KernelParams& p, const __nv_bfloat16* stage, int rl, int n,
-                                                 const uint4* own) {
-  float acc[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+// For two output vectors out[rl[u], nn[u]..+8): sum of the world_size bf16 partial vectors in
+// rank order, in fp32, plus the bias, rounded once.  This rank's own partials come from
+// registers (`own`), the peers' from the staging buffer; all 2 x (world - 1) loads are
+// issued before the first use.
+__device__ __forceinline__ void reduce_partials2(const KernelParams& p, const __nv_bfloat16* stage, const int (&rl)[2],
+                                                 const int (&nn)[2], const bool (&live)[2], const uint4 (&own)[2],
+                                                 uint4 (&res)[2]) {
   const size_t R = (size_t)p.rows_per_rank;
-  const int sources = p.world_size * p.splits;
-  for (int s0 = 0; s0 < sources; s0 += 8) {
-    uint4 vals[8];
+  float acc[2][8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int s = s0 + u;
-      if (s < sources) {
-        if (own != nullptr && s == p.rank) vals[u] = *own;
-        else vals[u] = __ldcg(reinterpret_cast<const uint4*>(stage + ((size_t)s * R + rl) * p.N + n));
-      } else {
-        vals[u] = make_uint4(0, 0, 0, 0);
+  for (int u = 0; u < 2; ++u)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+  for (int s0 = 0; s0 < p.world_size; s0 += 8) {
+    uint4 vals[2][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int s = s0 + k;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (s < p.world_size && s != p.rank && live[u]) {
+          vals[u][k] = __ldcg(reinterpret_cast<const uint4*>(stage + ((size_t)s * R + rl[u]) * p.N + nn[u]));
+        } else {
+          vals[u][k] = (s == p.rank) ? own[u] : make_uint4(0, 0, 0, 0);
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u][k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[u][2 * e] += f.x;
+          acc[u][2 * e + 1] += f.y;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    if (p.bias != nullptr && !p.bias_at_source && live[u]) {
+      const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + nn[u]);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __bfloat1622float2(h[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
+        acc[u][2 * e] = fmaf(f.x, p.bias_scale, acc[u][2 * e]);
+        acc[u][2 * e + 1] = fmaf(f.y, p.bias_scale, acc[u][2 * e + 1]);
       }
     }
+    res[u].x = pack_bf16x2(acc[u][0], acc[u][1]);
+    res[u].y = pack_bf16x2(acc[u][2], acc[u][3]);
+    res[u].z = pack_bf16x2(acc[u][4], acc[u][5]);
+    res[u].w = pack_bf16x2(acc[u][6], acc[u][7]);
   }
-  if (p.bias != nullptr && !p.bias_at_source) {
-    const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __bfloat1622float2(h[e]);
-      acc[2 * e] = fmaf(f.x, p.bias_scale, acc[2 * e]);
-      acc[2 * e + 1] = fmaf(f.y, p.bias_scale, acc[2 * e + 1]);
-    }
-  }
-  uint4 o;
-  o.x = pack_bf16x2(acc[0], acc[1]);
-  o.y = pack_bf16x2(acc[2], acc[3]);
-  o.z = pack_bf16x2(acc[4], acc[5]);
-  o.w = pack_bf16x2(acc[6], acc[7]);
-  return o;
 }
 
 // Reduce `items` 16-byte vectors of the block rows [r0, ...) x columns [c0, c0 + 8 * vec_per_row)
@@ -670,6 +679,37 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           __syncwarp();
           continue;
         }
+        if (owned) {
+          // ---- own tile: add the peers' staged rows to this rank's partial, two row segments
+          // per step so that 2 x (world - 1) loads are in flight per lane ----------------------
+          if (peers_ok) {
+#pragma unroll 1
+            for (int s = 0; s < kChunksPerRow; s += 2) {
+              uint4 own[2];
+              int rl[2], nn[2];
+              bool live[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int rr = (s + u) * kRowsPerStore + lane / kChunksPerRow;
+                const int cc = lane % kChunksPerRow;
+                const uint32_t addr = slab_addr(slab, rr, cc);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(own[u].x), "=r"(own[u].y), "=r"(own[u].z), "=r"(own[u].w)
+                             : "r"(addr));
+                rl[u] = m0 + rr - row_lo;
+                nn[u] = n0 + half * cols_per_pass + cc * 8;
+                live[u] = (m0 + rr < p.M) && (nn[u] < p.N);
+              }
+              uint4 res[2];
+              reduce_partials2(p, my_stage, rl, nn, live, own, res);
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+                if (live[u]) *reinterpret_cast<uint4*>(p.out + (size_t)rl[u] * p.N + nn[u]) = res[u];
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         // ---- slab -> global, whole row segments per store ------------------------------
 #pragma unroll 2
         for (int s = 0; s < kChunksPerRow; ++s) {
@@ -692,12 +732,6 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               *reinterpret_cast<uint4*>(dst) = val;
             } else if (direct) {
               *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n) = val;
-            } else if (owned) {
-              if (peers_ok) {
-                const int rl = m - row_lo;
-                *reinterpret_cast<uint4*>(p.out + (size_t)rl * p.N + n) =
-                    reduce_partials(p, my_stage, rl, n, &val);
-              }
             } else if (p.debug != 2) {
               const int owner = m / R;
               const int rl = m - owner * R;

@@ -78,7 +78,10 @@ class GemmRS:
         self.splits = 0  # 0 = chosen from the shape; else K slices per tile
         self.trace: Optional[torch.Tensor] = None  # int64 [160, 8]: per-CTA globaltimer stamps when set
         self.debug = 0  # measurement aids that make results wrong: 1 = stage locally, 2 = do not stage
-        self.fuse_own = False  # True: own tiles add the peers' rows in their epilogue instead of being staged
+        # True: a rank's own tiles add the peers' rows in their epilogue; False: own tiles are staged like
+        # the others and all CTAs reduce after the GEMM tiles; None: fused up to 4 ranks (few rows to
+        # fetch per tile), separate pass beyond
+        self.fuse_own: Optional[bool] = None
         self.tma_store = True  # staged tiles leave through TMA stores where the shape allows
         self.force_staged = False  # stage and reduce even on one rank (tests the staged path on one GPU)
 
@@ -133,7 +136,7 @@ class GemmRS:
             plan["splits"],
             self.trace,
             self.debug,
-            self.fuse_own,
+            (self.world_size <= 4) if self.fuse_own is None else bool(self.fuse_own),
             self.tma_store,
             self.force_staged,
         )

@@ -216,7 +216,7 @@ def test_gemm_staged_path_on_one_gpu(tma_store, fuse_own, m, n, k, block_n, cta_
         op.check()
     finally:
         op.block_n, op.cta_pair, op.splits = 0, -1, 0
-        op.force_staged, op.tma_store, op.fuse_own = False, True, False
+        op.force_staged, op.tma_store, op.fuse_own = False, True, None
     want = oracle.gemm_rs_fused_rounding([a], [w], bias, 0)
     assert oracle.outlier_fraction(out, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL) < 1e-4
     assert oracle.relative_error(out, a.float() @ w.float().T + bias.float()) < 5e-3
