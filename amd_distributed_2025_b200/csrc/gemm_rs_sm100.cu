@@ -788,8 +788,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               uint32_t* ctr = peer_ptr<uint32_t>(p.peer_base[o], p.off_counters) + base_index;
 #pragma unroll
               for (int w = 0; w < kEpilogueWarps; ++w) {
-                if (o == p.rank) red_release_gpu_add(ctr + w, 1u);
-                else red_release_sys_add(ctr + w, 1u);
+                // relaxed: the fence above already orders the tile's stores before these
+                if (o == p.rank) red_relaxed_gpu_add(ctr + w, 1u);
+                else red_relaxed_sys_add(ctr + w, 1u);
               }
             }
           }
@@ -953,8 +954,11 @@ GemmRsPlan make_plan(int M, int N, int K, int world_size, int sms, int force_bn,
     const int schedulers = std::max(sms / c.ctas, 1);
     const int tiles = ((m_tiles + c.ctas - 1) / c.ctas) * ((N + c.bn - 1) / c.bn);
     int max_splits = 1;
+    // Slices travel as fp32 and cost a fence and a counter per tile and owner: across GPUs they
+    // only pay when the problem leaves most of the machine idle.
+    const int idle_factor = world_size > 1 ? 4 : 2;
     if (force_splits > 0) max_splits = force_splits;
-    else if (tiles * 2 <= schedulers) max_splits = std::min(std::min(schedulers / tiles, num_kb / 4), 8);
+    else if (tiles * idle_factor <= schedulers) max_splits = std::min(std::min(schedulers / tiles, num_kb / 4), 8);
     for (int sp = (force_splits > 0 ? force_splits : 1); sp <= std::max(max_splits, 1); ++sp) {
       int per = (num_kb + sp - 1) / sp;
       if ((sp - 1) * per >= num_kb) continue;  // an empty slice

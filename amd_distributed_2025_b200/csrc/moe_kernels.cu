@@ -216,9 +216,9 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) moe_dispatch_kernel(const
   __syncthreads();
   if (is_last_shared) {
     if (tid == 0) {
-      __threadfence_system();
-      for (int dst = 0; dst < p.world_size; ++dst)
-        st_release_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_DATA, p.rank), p.epoch);
+      __threadfence_system();  // one fence orders every CTA's row stores (observed through the counter) ...
+      for (int dst = 0; dst < p.world_size; ++dst)  // ... before these relaxed flag stores
+        st_relaxed_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_DATA, p.rank), p.epoch);
       p.sync_counters[0] = 0;
       p.sync_counters[1] = 0;
     }
