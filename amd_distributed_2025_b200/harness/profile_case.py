@@ -1,0 +1,97 @@
+"""Run ONE small case of one kernel a few times on one GPU -- the workload to put under a
+profiler (``ncu -k regex:<kernel> -c <n> python -m ...profile_case ...``) or to trace with
+the kernels' own phase stamps.
+
+The cases are sized for profiling: operands a little larger than the 126 MB L2 so DRAM
+counters mean something, a few hundred MB on the device at most, a handful of launches.
+The reference has no profiling hooks (timing is left to an evaluator outside its tree,
+all2all/task.yml:6-8).
+
+Examples::
+
+    python -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --m 8192 --n 4096 --k 4096
+    python -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --m 2048 --n 2048 --k 2048 --staged
+    python -m amd_distributed_2025_b200.harness.profile_case --kernel moe --experts 256 --topk 8 --hidden 7168 --tokens 128
+    python -m amd_distributed_2025_b200.harness.profile_case --kernel fp8_gemm --m 4096 --n 4096 --k 4096
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+from .. import contract, oracle
+from ..utils import timing
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--kernel", choices=["gemm_rs", "moe", "fp8_gemm"], required=True)
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--staged", action="store_true", help="gemm_rs: run the multi-rank staging/reduction path on one GPU")
+    ap.add_argument("--trace", action="store_true", help="gemm_rs: print the per-CTA phase stamps of the last launch")
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--tokens", type=int, default=128)
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args(argv)
+    torch.cuda.set_device(0)
+    out = {"kernel": args.kernel}
+    if args.kernel == "gemm_rs":
+        from ..models import gemm_rs
+
+        a, w, bias = contract.make_gemm_rs_inputs(0, 1, args.m, args.n, args.k, True, 1, device="cuda")
+        op = gemm_rs.get_op(args.m, args.n, args.k)
+        op.force_staged = args.staged
+        if args.trace:
+            op.enable_trace(True)
+        times = timing.time_cuda(lambda: op(a, w, bias), warmup=1, iters=args.iters)
+        op.check()
+        y = op(a, w, bias)
+        out.update(shape=[args.m, args.n, args.k], plan=dict(op.plan(args.m, args.n, args.k)), us=[t * 1e3 for t in times],
+                   tflops=2.0 * args.m * args.n * args.k / min(times) / 1e9,
+                   rel_err=oracle.relative_error(y, a.float() @ w.float().T + bias.float()))
+        if args.trace:
+            tr = op.trace.cpu()
+            tr = tr[tr[:, 0] > 0]
+            rel = (tr - tr[:, 0].min()).float() / 1e3
+            out["trace_us_median"] = {"ready": float(rel[:, 1].median()), "gemm_done": float(rel[:, 2].median()),
+                                      "exit": float(rel[:, 3].median())}
+    elif args.kernel == "moe":
+        from ..models import moe_all2all
+
+        cfg, data, _, _ = contract.make_moe_inputs(args.experts, args.topk, args.hidden, args.tokens, 1, 0, 1, device="cuda",
+                                                   dtype=getattr(torch, args.dtype), fixed_num_tokens=args.tokens,
+                                                   weights="softmax")
+        fn = lambda: moe_all2all.custom_kernel((cfg, data, 0, 1))  # noqa: E731
+        times = timing.time_cuda(fn, warmup=1, iters=args.iters)
+        y = fn()
+        moe_all2all.get_layer(cfg, 0, 1).check()
+        ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, data, 1))
+        out.update(config=[args.experts, args.topk, args.hidden, args.tokens], us=[t * 1e3 for t in times], ok=ok, msg=msg)
+    else:
+        from ..ops.fp8_gemm import fp8_gemm, fp8_gemm_reference
+
+        a = torch.randn(args.m, args.k, device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn(args.n, args.k, device="cuda").to(torch.float8_e4m3fn)
+        kb, nb = (args.k + 127) // 128, (args.n + 127) // 128
+        a_s = torch.rand(args.m, kb, device="cuda") + 0.5
+        b_s = torch.rand(nb, kb, device="cuda") + 0.5
+        times = timing.time_cuda(lambda: fp8_gemm(a, b, a_s, b_s), warmup=1, iters=args.iters)
+        c = fp8_gemm(a, b, a_s, b_s)
+        out.update(shape=[args.m, args.n, args.k], us=[t * 1e3 for t in times],
+                   tflops=2.0 * args.m * args.n * args.k / min(times) / 1e9,
+                   rel_err=oracle.relative_error(c, fp8_gemm_reference(a, b, a_s, b_s)))
+    torch.cuda.synchronize()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

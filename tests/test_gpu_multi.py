@@ -107,10 +107,15 @@ def _gemm_rank(rank, world_size, shapes, repeats):
             ok2, msg2 = oracle.check_gemm_rs_output(y, lib)
             outliers = 0.0
         else:
+            # Same rounding chain (bf16 partials, fp32 sum): all but a handful of elements must agree
+            # within the task tolerance.  The library path also rounds after every hop of its ring,
+            # which with unit-variance operands alone moves about 1 % of its elements further than
+            # the tolerance from the exact sum, so it is only a loose sanity bound here.
             want = oracle.gemm_rs_fused_rounding(a_all, w_all, data[2], rank)
-            outliers = max(oracle.outlier_fraction(y, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL),
-                           oracle.outlier_fraction(y, lib, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL))
-            ok2, msg2 = outliers < 1e-3, f"{outliers:.2e} of the elements outside the task tolerance"
+            outliers = oracle.outlier_fraction(y, want, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL)
+            vs_lib = oracle.outlier_fraction(y, lib, oracle.GEMM_RS_RTOL, oracle.GEMM_RS_ATOL)
+            ok2 = outliers < 1e-3 and vs_lib < 3e-2
+            msg2 = f"{outliers:.2e} (same chain) / {vs_lib:.2e} (library) of the elements outside the task tolerance"
         out.append({"shape": [m, n, k, kind], "ok": bool(ok and ok2 and rel < 5e-3), "msg": msg or msg2, "rel": rel,
                     "outliers": outliers})
         del everyone
