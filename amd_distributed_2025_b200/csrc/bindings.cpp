@@ -128,6 +128,12 @@ void moe_dispatch(SymmHeap& heap, const at::Tensor& x, const at::Tensor& indices
   p.status = heap.status_device();
   p.count_blocks = (int32_t)count_blocks;
   p.chunk = (int32_t)chunk;
+  if (b200::moe_dispatch_small_applies((int)n, (int)num_experts)) {
+    // one warp per entry, at least one CTA per rank for the count broadcast, any number of CTAs
+    const int small_grid = (int)std::max<int64_t>(std::min<int64_t>((n + 7) / 8, 2 * max_blocks), std::max(ws, 1));
+    cuda_check(b200::launch_moe_dispatch_small(p, small_grid, at::cuda::getCurrentCUDAStream()), "moe_dispatch launch");
+    return;
+  }
   cuda_check(b200::launch_moe_dispatch(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dispatch launch");
 }
 

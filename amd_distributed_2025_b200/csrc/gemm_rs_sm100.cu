@@ -258,21 +258,28 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
         off[u] = ~(size_t)0;
       }
     }
-    for (int s = 0; s < sources; ++s) {
-      const __nv_bfloat16* src = stage + (size_t)s * R * p.N;
-      uint4 vals[U];
+    // two sources per step: 16 loads in flight per thread, added in rank order
+    for (int s = 0; s < sources; s += 2) {
+      const __nv_bfloat16* src0 = stage + (size_t)s * R * p.N;
+      const __nv_bfloat16* src1 = src0 + R * p.N;
+      const bool two = s + 1 < sources;
+      uint4 v0[U], v1[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        vals[u] = off[u] != ~(size_t)0 ? __ldcg(reinterpret_cast<const uint4*>(src + off[u])) : make_uint4(0, 0, 0, 0);
+        const bool live = off[u] != ~(size_t)0;
+        v0[u] = live ? __ldcg(reinterpret_cast<const uint4*>(src0 + off[u])) : make_uint4(0, 0, 0, 0);
+        v1[u] = (live && two) ? __ldcg(reinterpret_cast<const uint4*>(src1 + off[u])) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vals[u]);
+        const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[u]);
+        const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[u]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h[e]);
-          acc[u][2 * e] += f.x;
-          acc[u][2 * e + 1] += f.y;
+          const float2 f0 = __bfloat1622float2(h0[e]);
+          const float2 f1 = __bfloat1622float2(h1[e]);
+          acc[u][2 * e] = (acc[u][2 * e] + f0.x) + f1.x;
+          acc[u][2 * e + 1] = (acc[u][2 * e + 1] + f0.y) + f1.y;
         }
       }
     }
@@ -826,8 +833,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // ================================ reduction of staged tiles =============================
   // Tiles that straddle an ownership boundary (always the case when a rank owns fewer than
   // 128 rows) and all tiles of a K-sliced problem were staged by every (virtual) rank, this
-  // one included.  The unit of work is one 128 x BN tile (four counters, one per 32-row
-  // quarter); unit j is reduced by CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles
+  // one included.  Unit j is reduced by CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles
   // start first.
   const int R = p.rows_per_rank;
   const int row_lo = p.rank * R;
@@ -836,38 +842,47 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const uint32_t want = (uint32_t)(p.world_size * p.splits);
   uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
   const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
+  // Unit of work: a whole 128 x BN tile (four counters) when there are plenty of tiles, else one
+  // 32-row quarter of a tile (one counter) so that a small problem still occupies every CTA.
+  int staged_tiles = 0;
+  for (int mb = mb_lo; mb <= mb_hi; ++mb)
+    if (!tile_owned(p, mb)) staged_tiles += p.n_tiles;
+  const int parts = (staged_tiles >= 2 * G) ? 1 : kEpilogueWarps;  // units per tile
+  const int rows_per_part = BM / parts;
+  const int ctrs_per_part = kEpilogueWarps / parts;
   int j = 0;
   for (int mb = mb_lo; mb <= mb_hi; ++mb) {
     if (tile_owned(p, mb)) continue;
-    for (int nb = 0; nb < p.n_tiles; ++nb, ++j) {
-      if (j % G != G - 1 - (int)blockIdx.x) continue;
-      // one counter per 32-row quarter of the tile: four threads wait in parallel
-      uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps;
-      if (tid == 0) wait_ok_shared = 1;
-      __syncthreads();
-      if (tid < kEpilogueWarps) {
-        if (!wait_u32_ge(ctr + tid, want, limit, p.status, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb,
-                         p.world_size > 1))
-          wait_ok_shared = 0;
-      }
-      __syncthreads();
-      const bool ok = wait_ok_shared != 0;
-      const int r0 = max(mb * BM, row_lo);
-      const int r1 = min(min((mb + 1) * BM, row_lo + R), p.M);
-      if (ok && r1 > r0) {
-        const int c0 = nb * BN;
-        const int c1 = min(c0 + BN, p.N);
-        const int vec_per_row = (c1 - c0) >> 3;
-        if (p.splits > 1) {
-          reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
-                              (r1 - r0) * vec_per_row, tid);
-        } else {
-          reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
+    for (int nb = 0; nb < p.n_tiles; ++nb) {
+      for (int part = 0; part < parts; ++part, ++j) {
+        if (j % G != G - 1 - (int)blockIdx.x) continue;
+        const int r0 = max(mb * BM + part * rows_per_part, row_lo);
+        const int r1 = min(min(mb * BM + (part + 1) * rows_per_part, row_lo + R), p.M);
+        uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps + part * ctrs_per_part;
+        if (tid == 0) wait_ok_shared = 1;
+        __syncthreads();
+        if (tid < ctrs_per_part) {
+          if (!wait_u32_ge(ctr + tid, want, limit, p.status, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb,
+                           p.world_size > 1))
+            wait_ok_shared = 0;
         }
+        __syncthreads();
+        const bool ok = wait_ok_shared != 0;
+        if (ok && r1 > r0) {
+          const int c0 = nb * BN;
+          const int c1 = min(c0 + BN, p.N);
+          const int vec_per_row = (c1 - c0) >> 3;
+          if (p.splits > 1) {
+            reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
+                                (r1 - r0) * vec_per_row, tid);
+          } else {
+            reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
+          }
+        }
+        __syncthreads();
+        if (tid < ctrs_per_part) ctr[tid] = 0;  // this parity's counters are next used two calls from now
+        if (!ok) return;
       }
-      __syncthreads();
-      if (tid < kEpilogueWarps) ctr[tid] = 0;  // this parity's counters are next used two calls from now
-      if (!ok) return;
     }
   }
   trace_stamp(p, 3);

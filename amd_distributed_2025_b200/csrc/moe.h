@@ -58,6 +58,12 @@ int moe_dispatch_max_blocks(int device);
 
 cudaError_t launch_moe_dispatch(const MoeDispatchParams& p, int grid, cudaStream_t stream);
 
+// Variant for small problems (a few thousand (token, k) entries): same protocol and layouts,
+// but every CTA derives the slots from the full index list, so there is no in-GPU barrier.
+// blk_hist, local_rank, count_blocks and chunk of the parameters are not used.
+bool moe_dispatch_small_applies(int num_entries, int num_experts);
+cudaError_t launch_moe_dispatch_small(const MoeDispatchParams& p, int grid, cudaStream_t stream);
+
 // expert_y[e, j, :] = cast(expert_x[e, j, :]) * scale for j < expert_num_tokens[e];
 // padding rows are not touched (all2all/reference.py:262 scales the padded buffer too,
 // but only valid rows are ever read back).

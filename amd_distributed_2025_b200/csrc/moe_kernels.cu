@@ -229,6 +229,148 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) moe_dispatch_kernel(const
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// dispatch, small problems (decode): no in-GPU barrier
+// ---------------------------------------------------------------------------------------
+// With a few thousand (token, k) entries every CTA can afford to read ALL of them: it builds
+// the full per-expert histogram in shared memory itself and finds an entry's position among
+// equal experts by scanning the entries before it.  That removes the per-chunk counting
+// pass, the grid-wide barrier and the histogram round trip through global memory from the
+// latency chain; the cross-GPU protocol (count rows, flags, row stores, done flags) is the
+// same as in moe_dispatch_kernel, and so are the resulting layouts.
+__global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_small_kernel(const MoeDispatchParams p) {
+  extern __shared__ int32_t smem_small[];  // [n] expert ids (or -1), then [num_experts] histogram
+  __shared__ int is_last_shared;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int n = p.num_tokens * p.k;
+  const int E = p.num_experts;
+  const int G = gridDim.x;
+  const uint64_t my_base = p.peer_base[p.rank];
+  int32_t* s_idx = smem_small;
+  int32_t* s_hist = smem_small + ((n + 31) & ~31);
+
+  for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
+  for (int i = tid; i < n; i += blockDim.x) {
+    int e = p.indices[i];
+    if (e < 0 || e >= E) {
+      if (blockIdx.x == 0) record_status(p.status, STATUS_BAD_INDEX, PHASE_NONE, -1, i, p.epoch, (uint64_t)(int64_t)e);
+      e = -1;
+    }
+    s_idx[i] = e;
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += blockDim.x) {
+    const int e = s_idx[i];
+    if (e >= 0) atomicAdd(&s_hist[e], 1);
+  }
+  __syncthreads();
+
+  // publish this rank's per-expert totals to every rank, then collect theirs
+  for (int dst = blockIdx.x; dst < p.world_size; dst += G) {
+    int32_t* remote = peer_ptr<int32_t>(p.peer_base[dst], p.layout.off_counts) + (size_t)p.rank * E;
+    for (int e = tid; e < E; e += blockDim.x) remote[e] = s_hist[e];
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      st_release_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_COUNTS, p.rank), p.epoch);
+    }
+  }
+  if (tid < p.world_size) {
+    wait_flag_ge(flag_ptr(my_base, FLAG_MOE_COUNTS, tid), p.epoch, p.timeout_ns, p.status, PHASE_MOE_COUNTS,
+                 tid, (int)blockIdx.x);
+  }
+  __syncthreads();
+  const int32_t* counts = peer_ptr<const int32_t>(my_base, p.layout.off_counts);  // [world][E]
+
+  if (blockIdx.x == 0) {
+    for (int el = tid; el < p.num_local_experts; el += blockDim.x) {
+      int total = 0;
+      for (int s = 0; s < p.world_size; ++s)
+        total += __ldcg(counts + (size_t)s * E + p.rank * p.num_local_experts + el);
+      p.expert_num_tokens[el] = min(total, p.max_recv);
+    }
+  }
+
+  if (!status_timed_out(p.status)) {
+    const int warps_total = G * (kDispatchThreads / 32);
+    const uint8_t* xbytes = reinterpret_cast<const uint8_t*>(p.x);
+    for (int i = blockIdx.x * (kDispatchThreads / 32) + warp; i < n; i += warps_total) {
+      const int e = s_idx[i];
+      if (e < 0) {
+        if (lane == 0) p.route[i] = make_int2(-1, -1);
+        continue;
+      }
+      // entries of this rank with the same expert that come before entry i, plus the rows
+      // that lower ranks send to that expert: the slot in the reference's order
+      int part = 0;
+      for (int j = lane; j < i; j += 32) part += (s_idx[j] == e) ? 1 : 0;
+      if (lane < p.rank) part += __ldcg(counts + (size_t)lane * E + e);
+      const int slot = warp_sum(part);
+      const int dst = e / p.num_local_experts;
+      const int el = e - dst * p.num_local_experts;
+      if (slot >= p.max_recv) {
+        if (lane == 0) {
+          record_status(p.status, STATUS_BAD_INDEX, PHASE_NONE, dst, i, p.epoch, (uint64_t)(int64_t)slot);
+          p.route[i] = make_int2(-1, -1);
+        }
+        continue;
+      }
+      const int64_t row = (int64_t)el * p.max_recv + slot;
+      const int t = i / p.k;
+      const int kk = i - t * p.k;
+      const uint64_t dst_base = p.peer_base[dst];
+      warp_copy_row(xbytes + (size_t)t * p.row_bytes,
+                    peer_ptr<uint8_t>(dst_base, p.layout.off_expert_x) + (size_t)row * p.row_bytes, p.row_bytes,
+                    lane);
+      if (lane < kMetaDim) {
+        int32_t mv = 0;
+        if (lane == 0) mv = e;
+        else if (lane == 1) mv = p.rank;
+        else if (lane == 2) mv = t;
+        else if (lane == 3) mv = kk;
+        peer_ptr<int32_t>(dst_base, p.layout.off_expert_meta)[(size_t)row * kMetaDim + lane] = mv;
+      }
+      if (lane == 0) p.route[i] = make_int2(dst, (int)row);
+    }
+  }
+
+  // when every CTA has delivered, tell the owners; wait for theirs
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    const uint32_t done = atomicAdd(&p.sync_counters[1], 1u);
+    is_last_shared = (done == (uint32_t)G - 1u);
+  }
+  __syncthreads();
+  if (is_last_shared) {
+    if (tid == 0) {
+      __threadfence_system();
+      for (int dst = 0; dst < p.world_size; ++dst)
+        st_relaxed_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_DATA, p.rank), p.epoch);
+      p.sync_counters[1] = 0;
+    }
+    if (tid < p.world_size) {
+      wait_flag_ge(flag_ptr(my_base, FLAG_MOE_DATA, tid), p.epoch, p.timeout_ns, p.status, PHASE_MOE_DATA, tid,
+                   (int)blockIdx.x);
+    }
+  }
+}
+
+bool moe_dispatch_small_applies(int num_entries, int num_experts) {
+  return num_entries <= 4096 && num_experts <= 4096;
+}
+
+cudaError_t launch_moe_dispatch_small(const MoeDispatchParams& p, int grid, cudaStream_t stream) {
+  const int n = p.num_tokens * p.k;
+  const size_t smem = ((size_t)((n + 31) & ~31) + (size_t)p.num_experts) * sizeof(int32_t);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  moe_dispatch_small_kernel<<<grid, kDispatchThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
 int moe_dispatch_max_blocks(int device) {
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
