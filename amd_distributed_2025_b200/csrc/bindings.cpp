@@ -14,6 +14,7 @@
 
 #include "fp8_gemm.h"
 #include "gemm_rs.h"
+#include "host_shm_heap.h"
 #include "moe.h"
 #include "status.h"
 #include "symm_heap.h"
@@ -335,6 +336,44 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                    "wait_selftest launch");
       });
 
+  py::class_<b200::HostShmHeap, std::shared_ptr<b200::HostShmHeap>>(m, "HostShmHeap")
+      .def(py::init([](const std::string& prefix, int rank, int world_size, int64_t bytes) {
+             return std::make_shared<b200::HostShmHeap>(prefix, rank, world_size, (uint64_t)bytes);
+           }),
+           py::arg("prefix"), py::arg("rank"), py::arg("world_size"), py::arg("bytes"))
+      .def("open_peers", [](b200::HostShmHeap& h, int64_t timeout_ns) { return h.open_peers((uint64_t)timeout_ns); })
+      .def("close", &b200::HostShmHeap::close)
+      .def("signal", [](b200::HostShmHeap& h, int row, int dst, int64_t epoch) { h.signal(row, dst, (uint64_t)epoch); })
+      .def("wait",
+           [](b200::HostShmHeap& h, int row, int src, int64_t epoch, int64_t timeout_ns) {
+             py::gil_scoped_release release;
+             b200::StatusWord w = h.wait(row, src, (uint64_t)epoch, (uint64_t)timeout_ns, b200::PHASE_TEST);
+             py::gil_scoped_acquire acquire;
+             return status_to_dict(w);
+           })
+      .def("barrier",
+           [](b200::HostShmHeap& h, int64_t epoch, int64_t timeout_ns) {
+             py::gil_scoped_release release;
+             b200::StatusWord w = h.barrier((uint64_t)epoch, (uint64_t)timeout_ns);
+             py::gil_scoped_acquire acquire;
+             return status_to_dict(w);
+           })
+      .def("status", [](const b200::HostShmHeap& h) { return status_to_dict(h.last_status()); })
+      .def("reset_status", &b200::HostShmHeap::reset_status)
+      .def("view",
+           [](b200::HostShmHeap& h, int r, int64_t offset, std::vector<int64_t> shape, at::ScalarType dtype) {
+             int64_t numel = 1;
+             for (auto s : shape) numel *= s;
+             const int64_t nbytes = numel * (int64_t)c10::elementSize(dtype);
+             TORCH_CHECK(r >= 0 && r < h.world_size() && h.base(r) != nullptr, "rank ", r, " is not mapped");
+             TORCH_CHECK(offset >= (int64_t)b200::kHeapHeaderBytes && (uint64_t)(offset + nbytes) <= h.bytes(),
+                         "view outside the payload area of the slab");
+             return at::from_blob(h.base(r) + offset, shape, at::TensorOptions().dtype(dtype).device(at::kCPU));
+           },
+           py::arg("rank"), py::arg("offset"), py::arg("shape"), py::arg("dtype"));
+
+  m.attr("FLAG_BARRIER") = (int)b200::FLAG_BARRIER;
+  m.attr("FLAG_TEST") = (int)b200::FLAG_TEST;
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_expert_scale", &moe_expert_scale);
   m.def("moe_combine", &moe_combine);

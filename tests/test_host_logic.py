@@ -1,0 +1,114 @@
+"""CPU tests of the host-side logic: slab layouts, epochs, the GEMM planner, status decoding,
+timing and roofline helpers.  The native extension is built if it is missing (nvcc
+cross-compiles without a GPU); nothing here launches a kernel."""
+import math
+
+import pytest
+import torch
+
+from amd_distributed_2025_b200 import contract
+from amd_distributed_2025_b200.parallel.symm_mem import EpochCounter, SlabLayout
+from amd_distributed_2025_b200.utils import roofline, timing
+from amd_distributed_2025_b200.utils.status import StatusError, describe_status
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from amd_distributed_2025_b200.ops import _ext
+
+    return _ext.load()
+
+
+def test_slab_layout_is_deterministic_aligned_and_disjoint():
+    a, b = SlabLayout(4096), SlabLayout(4096)
+    for lay in (a, b):
+        lay.add("counts", 8 * 256 * 4)
+        lay.add("meta", 32 * 2048 * 5 * 4)
+        lay.add("x", 32 * 2048 * 7168 * 2)
+    assert a.regions == b.regions  # every rank derives the same offsets without talking
+    assert not a.overlaps()
+    assert all(off % 1024 == 0 and off >= 4096 for off, _ in a.regions.values())
+    assert a.total_bytes >= max(off + size for off, size in a.regions.values())
+    with pytest.raises(KeyError):
+        a.add("x", 16)
+
+
+def test_moe_slab_layout_sizes_match_the_dispatch_contract():
+    from amd_distributed_2025_b200.models.moe_all2all import moe_slab_layout
+
+    cfg = contract.MoEConfig(256, 8, 7168, 256, torch.bfloat16, torch.bfloat16)
+    lay = moe_slab_layout(cfg, 8, 4096)
+    rows = 32 * 2048  # E_local * max_recv
+    assert lay.size("expert_x") == rows * 7168 * 2 and lay.size("expert_y") == rows * 7168 * 2
+    assert lay.size("expert_meta") == rows * 5 * 4 and lay.size("counts") == 8 * 256 * 4
+    assert not lay.overlaps()
+
+
+def test_epochs_only_grow_per_protocol():
+    e = EpochCounter()
+    assert [e.next("a"), e.next("a"), e.next("b"), e.next("a")] == [1, 2, 1, 3]
+    assert e.current("a") == 3 and e.current("missing") == 0
+
+
+def test_status_decoding():
+    st = {"code": 1, "phase": 5, "peer": 3, "detail": 17, "epoch": 9, "seen": 2}
+    text = describe_status(st, rank=4)
+    assert "timeout" in text and "rs_partials" in text and "rank 4" in text
+    err = StatusError(text, st)
+    assert err.code == "timeout" and err.phase == "rs_partials" and err.status["peer"] == 3
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+def test_gemm_plan_is_valid_for_all_task_shapes(ext, ws):
+    specs = contract.task_specs("gemm_rs", "tests") + contract.task_specs("gemm_rs", "benchmarks")
+    specs += [dict(m=c["m"], n=c["n"], k=c["k"]) for c in contract.load_task("headline")["gemm_rs"]]
+    for s in specs:
+        if s["m"] % ws or s["k"] % ws:
+            continue
+        m, n, k = s["m"], s["n"], s["k"] // ws
+        plan = ext.gemm_rs_plan(m, n, k, ws, 0, -1, 0)
+        assert plan == ext.gemm_rs_plan(m, n, k, ws, 0, -1, 0)  # pure function: all ranks agree
+        assert plan["block_n"] in (64, 128, 192, 256) and plan["cta_pair"] in (0, 1)
+        if plan["cta_pair"]:
+            assert plan["block_n"] != 64
+        num_kb = (k + 63) // 64
+        sp = plan["splits"]
+        assert 1 <= sp <= 8 and (sp - 1) * math.ceil(num_kb / sp) < num_kb  # no empty K slice
+        assert plan["stage_bytes"] == (m * n * 2 if sp == 1 else sp * m * n * 4)
+        assert plan["counter_bytes"] >= math.ceil(m / 128) * math.ceil(n / 64) * 4 * 4
+
+
+def test_gemm_plan_honours_overrides_and_prefers_pairs_for_large_problems(ext):
+    assert ext.gemm_rs_plan(8192, 8192, 3584, 8, 0, -1, 0)["cta_pair"] == 1
+    assert ext.gemm_rs_plan(8192, 8192, 3584, 8, 0, -1, 0)["splits"] == 1
+    forced = ext.gemm_rs_plan(2048, 2048, 2048, 1, 128, 0, 2)
+    assert (forced["block_n"], forced["cta_pair"], forced["splits"]) == (128, 0, 2)
+    # a problem that leaves most SMs idle gets its K cut on one GPU
+    assert ext.gemm_rs_plan(256, 5120, 12800, 1, 0, -1, 0)["splits"] > 1
+
+
+def test_noalloc_entry_point_is_exported(ext):
+    import ctypes
+
+    lib = ctypes.CDLL(ext.__file__)
+    assert hasattr(lib, "b200_moe_dispatch_noalloc") and hasattr(lib, "b200_moe_dispatch_noalloc_status")
+
+
+def test_geomean_and_summaries():
+    assert timing.geomean([1.0, 100.0]) == pytest.approx(10.0)
+    assert math.isnan(timing.geomean([]))
+    s = timing.summarize([3.0, 1.0, 2.0])
+    assert s["min_ms"] == 1.0 and s["median_ms"] == 2.0 and s["n"] == 3
+
+
+def test_roofline_arithmetic():
+    peaks = {"bf16_tflops": 1600.0, "bf16_tflops_sustained": 1400.0, "nvlink_gbs_per_dir": 770.0}
+    r = roofline.gemm_rs_roofline_us(8192, 8192, 28672, 8, peaks)
+    assert r["flops"] == pytest.approx(2 * 8192 * 8192 * 3584)
+    assert r["compute_us"] == pytest.approx(r["flops"] / 1400e12 * 1e6)
+    assert r["link_bytes"] == pytest.approx(7 / 8 * 8192 * 8192 * 2)
+    assert r["roofline_us"] == max(r["compute_us"], r["link_us"])
+    m = roofline.moe_roofline_us(896, 896, 14336, peaks)
+    assert m["roofline_us"] == pytest.approx(2 * 896 * 14336 / 770e9 * 1e6)
+    loaded = roofline.load_peaks()
+    assert loaded["source"] in ("measured", "fallback") and loaded["hbm_gbs"] > 1000
