@@ -13,14 +13,21 @@ Examples::
     python -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --m 2048 --n 2048 --k 2048 --staged
     python -m amd_distributed_2025_b200.harness.profile_case --kernel moe --experts 256 --topk 8 --hidden 7168 --tokens 128
     python -m amd_distributed_2025_b200.harness.profile_case --kernel fp8_gemm --m 4096 --n 4096 --k 4096
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --m 8192 --n 8192 --k 28672 --trace
+
+Under ``torch.distributed.run`` the gemm_rs case runs on all ranks (``--k`` is the global K, split
+evenly) and every rank prints its own line; ``--trace`` adds the in-kernel phase stamps.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 import torch
+import torch.distributed as dist
 
 from .. import contract, oracle
 from ..utils import timing
@@ -40,29 +47,51 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=128)
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--fuse-own", choices=["auto", "on", "off"], default="auto",
+                    help="gemm_rs on several ranks: finish own tiles in their epilogue, or in a pass after the GEMM tiles")
     args = ap.parse_args(argv)
-    torch.cuda.set_device(0)
-    out = {"kernel": args.kernel}
+    rank, ws = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if ws > 1:
+        if args.kernel != "gemm_rs":
+            raise SystemExit("only the gemm_rs case runs on several ranks")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    out = {"kernel": args.kernel, "rank": rank, "world_size": ws}
     if args.kernel == "gemm_rs":
         from ..models import gemm_rs
 
-        a, w, bias = contract.make_gemm_rs_inputs(0, 1, args.m, args.n, args.k, True, 1, device="cuda")
-        op = gemm_rs.get_op(args.m, args.n, args.k)
+        k_local = args.k // ws
+        a, w, bias = contract.make_gemm_rs_inputs(rank, ws, args.m, args.n, args.k, True, 1, device="cuda")
+        op = gemm_rs.get_op(args.m, args.n, k_local)
         op.force_staged = args.staged
+        op.fuse_own = {"auto": None, "on": True, "off": False}[args.fuse_own]
         if args.trace:
             op.enable_trace(True)
-        times = timing.time_cuda(lambda: op(a, w, bias), warmup=1, iters=args.iters)
+        times = timing.time_cuda(lambda: op(a, w, bias), warmup=3 if ws > 1 else 1, iters=args.iters,
+                                 barrier=dist.barrier if ws > 1 else None)
         op.check()
+        if args.trace:
+            op.trace.zero_()
         y = op(a, w, bias)
-        out.update(shape=[args.m, args.n, args.k], plan=dict(op.plan(args.m, args.n, args.k)), us=[t * 1e3 for t in times],
-                   tflops=2.0 * args.m * args.n * args.k / min(times) / 1e9,
-                   rel_err=oracle.relative_error(y, a.float() @ w.float().T + bias.float()))
+        torch.cuda.synchronize()
+        out.update(shape=[args.m, args.n, args.k], plan=dict(op.plan(args.m, args.n, k_local)), us=[t * 1e3 for t in times],
+                   tflops_per_gpu=2.0 * args.m * args.n * k_local / min(times) / 1e9)
+        if ws == 1:
+            out["rel_err"] = oracle.relative_error(y, a.float() @ w.float().T + bias.float())
         if args.trace:
             tr = op.trace.cpu()
             tr = tr[tr[:, 0] > 0]
-            rel = (tr - tr[:, 0].min()).float() / 1e3
-            out["trace_us_median"] = {"ready": float(rel[:, 1].median()), "gemm_done": float(rel[:, 2].median()),
-                                      "exit": float(rel[:, 3].median())}
+            t0 = tr[:, 0].min()
+            names = {1: "pipeline_ready", 4: "first_own_tile", 5: "peers_rows_arrived", 6: "last_own_tile_stored",
+                     2: "gemm_tiles_done", 3: "exit"}
+            stamps = {}
+            for col, name in names.items():
+                c = tr[:, col]
+                c = c[c > 0]
+                if len(c):
+                    rel = (c - t0).float() / 1e3
+                    stamps[name] = [round(float(rel.min()), 1), round(float(rel.median()), 1), round(float(rel.max()), 1)]
+            out["trace_us_min_median_max"] = stamps
     elif args.kernel == "moe":
         from ..models import moe_all2all
 
@@ -89,7 +118,10 @@ def main(argv=None) -> int:
                    tflops=2.0 * args.m * args.n * args.k / min(times) / 1e9,
                    rel_err=oracle.relative_error(c, fp8_gemm_reference(a, b, a_s, b_s)))
     torch.cuda.synchronize()
-    print(json.dumps(out))
+    print(json.dumps(out), flush=True)
+    if ws > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 
