@@ -4,16 +4,17 @@
 // weight[N, K/ws], the result is sum_r input_r * weight_r^T (+ bias) scattered along M so
 // that rank r keeps rows [r*M/ws, (r+1)*M/ws).  The reference runs three serial stages
 // (library GEMM, elementwise bias, library reduce-scatter).  Here ONE persistent kernel
-//   * computes 128 x BN output tiles with tcgen05.mma (bf16 in, fp32 accumulators in
-//     tensor memory), operands staged by TMA into 128B-swizzled shared memory through an
-//     mbarrier pipeline, two accumulator buffers so the epilogue of a tile overlaps the
-//     main loop of the next;
-//   * in the epilogue rounds each partial row to bf16 (the reference's rounding point)
-//     and stores it into the *owning* rank's staging slot over NVLink, then bumps that
-//     owner's arrival counter for the tile -- tiles are visited so that the rows a rank
-//     owns itself come last;
-//   * finally reduces the world_size partials of its own rows in fixed rank order in
-//     fp32, adds the bias once with its multiplicity, rounds once and writes out[M/ws, N].
+//   * computes 128 x BN tiles (single CTAs) or 256 x BN tiles (CTA pairs, cta_group::2) with
+//     tcgen05.mma (bf16 in, fp32 accumulators in tensor memory), operands staged by plain
+//     TMA loads into 128B-swizzled shared memory through an mbarrier pipeline, two
+//     accumulator buffers so the epilogue of a tile overlaps the main loop of the next;
+//   * in the epilogue rounds each partial row to bf16 (the reference's rounding point) and
+//     stores it into the *owning* rank's staging slot over NVLink (TMA stores), then bumps
+//     that owner's arrival counters -- tiles are visited so that the rows a rank owns
+//     itself come last;
+//   * reduces the world_size partials of its own rows in fixed rank order in fp32, adds the
+//     bias with its multiplicity, rounds once and writes out[M/ws, N].
+// Small problems are cut along K into slices that travel as fp32 "virtual ranks".
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

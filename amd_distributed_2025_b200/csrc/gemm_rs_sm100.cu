@@ -8,12 +8,21 @@
 //   warp 0        TMA producer: fills a ring of shared-memory stages with A and W tiles
 //   warp 1        MMA issuer: one lane issues tcgen05.mma, accumulating in tensor memory;
 //                 also owns the tensor-memory allocation
-//   warps 2..5    epilogue: tcgen05.ld the accumulator, round to bf16, transpose through
-//                 shared memory so that every warp store covers whole 256-byte row
-//                 segments, store to the owner's staging buffer (peer memory)
+//   warps 2..5    epilogue: tcgen05.ld the accumulator, round to bf16, transpose through a
+//                 double-buffered, 128-byte-swizzled shared-memory slab, then either TMA-store
+//                 the rows into the owner's staging block (peer memory; asynchronous, so NVLink
+//                 back-pressure never stalls the warp) or store them per lane as whole
+//                 256-byte row segments (direct output, mixed-ownership tiles, fp32 slices)
 //   warp 6        signaller: after a tile's rows are stored, fences once and bumps the
 //                 owners' arrival counters, keeping that latency off the epilogue warps
-// After its share of GEMM tiles every CTA joins the reduction of this rank's own rows.
+// A rank's own rows are finished either in the epilogue of its own tiles (peers' staged rows
+// added there) or, by default beyond 4 ranks, in a reduction pass that every CTA joins after
+// its share of GEMM tiles; tiles that straddle an ownership boundary and K-sliced problems
+// always take the pass.
+//
+// Staging buffers and counters exist in two parities that calls alternate between.  A rank
+// reaches call n+2 only after it received every peer's partials of call n+1, so every peer
+// has started call n+1 and hence finished reading parity n%2: no barrier between calls.
 //
 // Every wait (mbarrier or peer counter) is bounded; on expiry the kernel records a status,
 // lets copies in flight land, frees tensor memory and returns.
