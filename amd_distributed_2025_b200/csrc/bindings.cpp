@@ -311,6 +311,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              h.open_peers(hs);
            })
       .def("close", &SymmHeap::close)
+      .def("close_peers", &SymmHeap::close_peers)
       .def_property_readonly("rank", &SymmHeap::rank)
       .def_property_readonly("world_size", &SymmHeap::world_size)
       .def_property_readonly("device", &SymmHeap::device)

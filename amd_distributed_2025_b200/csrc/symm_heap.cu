@@ -87,7 +87,7 @@ void SymmHeap::open_peers(const std::vector<std::string>& handles) {
   peers_open_ = true;
 }
 
-void SymmHeap::close() {
+void SymmHeap::close_peers() {
   if (base_[rank_] == nullptr) return;
   DeviceGuard guard(device_);
   cudaDeviceSynchronize();
@@ -96,6 +96,13 @@ void SymmHeap::close() {
     cudaIpcCloseMemHandle(base_[r]);
     base_[r] = nullptr;
   }
+  if (world_ > 1) peers_open_ = false;
+}
+
+void SymmHeap::close() {
+  if (base_[rank_] == nullptr) return;
+  close_peers();
+  DeviceGuard guard(device_);
   cudaFree(base_[rank_]);
   base_[rank_] = nullptr;
   if (status_dev_) cudaFree(status_dev_);

@@ -32,8 +32,11 @@ class SymmHeap {
   std::string ipc_handle() const;
   // Maps the peers' slabs.  handles[r] is rank r's ipc_handle(); the own entry is ignored.
   void open_peers(const std::vector<std::string>& handles);
-  // Unmaps peers and frees the slab.  All ranks must have stopped using it.
+  // Unmaps peers and frees the slab.  All ranks must have stopped using it.  Ranks that
+  // tear down together should call close_peers() first, meet on the host, then close():
+  // a slab must not be freed while a peer still maps it.
   void close();
+  void close_peers();
 
   int rank() const { return rank_; }
   int world_size() const { return world_; }

@@ -211,7 +211,18 @@ def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup
             if spec["m"] % world_size or spec["k"] % world_size:
                 continue
             results.append(eval_gemm_rs_shape(rank, world_size, spec, impl, mode, warmup, iters))
+    release_workspaces()
     return results
+
+
+def release_workspaces() -> None:
+    """Collective, orderly teardown of every cached symmetric workspace of this process."""
+    from ..models import gemm_rs, moe_all2all
+
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    moe_all2all.release_layers()
+    gemm_rs.release_ops()
 
 
 def summarize_results(results: List[Dict[str, Any]]) -> Dict[str, Any]:

@@ -151,8 +151,8 @@ class GemmRS:
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
 
-    def close(self) -> None:
-        self.ws.close()
+    def close(self, collective: bool = False) -> None:
+        self.ws.close(collective)
 
 
 _OPS: Dict[tuple, GemmRS] = {}
@@ -185,7 +185,7 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
         torch.cuda.synchronize()
         if initialized:
             dist.barrier(group=group)
-        op.close()
+        op.close(collective=True)
         need_stage, need_counters = max(need_stage, op.stage_bytes), max(need_counters, op.counter_bytes)
     op = GemmRS(need_stage, need_counters, group=group)
     _OPS[key] = op
@@ -193,8 +193,9 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
 
 
 def release_ops() -> None:
+    """Free every cached workspace (collective: all ranks must call it while idle)."""
     for op in _OPS.values():
-        op.close()
+        op.close(collective=True)
     _OPS.clear()
 
 

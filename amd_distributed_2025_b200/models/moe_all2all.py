@@ -204,8 +204,8 @@ class MoEAllToAll:
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
 
-    def close(self) -> None:
-        self.ws.close()
+    def close(self, collective: bool = False) -> None:
+        self.ws.close(collective)
 
 
 # --------------------------------------------------------------------------------------
@@ -241,7 +241,7 @@ def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None) -> MoEAllT
 def release_layers() -> None:
     """Free every cached workspace (collective: all ranks must call it while idle)."""
     for layer in _LAYERS.values():
-        layer.close()
+        layer.close(collective=True)
     _LAYERS.clear()
 
 

@@ -152,7 +152,14 @@ class SymmetricWorkspace:
     def reset_status(self) -> None:
         self.heap.reset_status()
 
-    def close(self) -> None:
-        if not self._closed:
-            self._closed = True
-            self.heap.close()
+    def close(self, collective: bool = False) -> None:
+        """Release the slab.  With ``collective=True`` (all ranks call it together, idle) the
+        peers' mappings are dropped first and the ranks meet on the host before anybody frees
+        its slab, so no slab is freed while a peer still maps it."""
+        if self._closed:
+            return
+        self._closed = True
+        if collective and self.world_size > 1 and dist.is_initialized():
+            self.heap.close_peers()
+            dist.barrier(group=self.group)
+        self.heap.close()

@@ -113,6 +113,13 @@ class Ours:
         for op in self.gemm._OPS.values():
             op.check(sync=True)
 
+    def release(self) -> None:
+        """Collective, orderly teardown of the symmetric workspaces (no slab is freed while a
+        peer still maps it)."""
+        torch.cuda.synchronize()
+        self.moe.release_layers()
+        self.gemm.release_ops()
+
 
 def _load_module(name: str, path: str, extra_path: str):
     sys.modules.pop("task", None)
@@ -159,6 +166,9 @@ class Reference:
         return self.grs.ref_kernel((dev_inputs["a"], item["w"], item["bias"]))
 
     def check(self) -> None:
+        pass
+
+    def release(self) -> None:
         pass
 
 
@@ -313,6 +323,7 @@ def main() -> int:
             "wall_s_timed_region": wall_dev,
         }
         print(json.dumps(line))
+    impl.release()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -54,6 +54,8 @@ def _moe_rank(rank, world_size, shapes, repeats):
         ok2, msg2 = oracle.check_moe_output(y, want)
         out.append({"shape": [E, k, H, T], "ok": bool(ok and ok2), "msg": msg or msg2, "layout_ok": bool(lay_ok),
                     "layout_msg": lay_msg})
+    torch.cuda.synchronize()
+    moe_all2all.release_layers()
     return out
 
 
@@ -119,6 +121,8 @@ def _gemm_rank(rank, world_size, shapes, repeats):
         out.append({"shape": [m, n, k, kind], "ok": bool(ok and ok2 and rel < 5e-3), "msg": msg or msg2, "rel": rel,
                     "outliers": outliers})
         del everyone
+    torch.cuda.synchronize()
+    gemm_rs.release_ops()
     return out
 
 
