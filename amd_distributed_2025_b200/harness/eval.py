@@ -59,6 +59,10 @@ def init_process_group(rank: int, world_size: int, backend: str, port: int, time
 def _worker(rank: int, world_size: int, backend: str, port: int, fn: Callable, args: tuple, result_dir: str) -> None:
     out: Dict[str, Any] = {"rank": rank, "ok": False}
     try:
+        if backend == "gloo":
+            # CPU ranks share the cores; leaving every rank at the default thread count makes
+            # the intra-op pools fight each other
+            torch.set_num_threads(max(1, (os.cpu_count() or world_size) // world_size))
         init_process_group(rank, world_size, backend, port)
         out["result"] = fn(rank, world_size, *args)
         out["ok"] = True
@@ -139,13 +143,20 @@ def eval_moe_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, 
     from ..models import moe_all2all
     from ..parallel import baseline_nccl
 
-    device = _device_for(rank)
+    device = torch.device(spec["device"]) if "device" in spec else _device_for(rank)
     cfg, mine, _, _ = moe_rank_data(spec, rank, world_size, device)
     data = (cfg, mine, rank, world_size)
-    fn = {
-        "ours": lambda: moe_all2all.custom_kernel(data),
-        "torch": lambda: baseline_nccl.moe_torch(data),
-    }[impl]
+    if impl == "reference":
+        from . import reference_arm
+
+        ref = reference_arm.load_all2all()
+        ref_data = reference_arm.moe_tuple(ref, cfg, mine, rank, world_size)
+        fn = lambda: ref.ref_kernel(ref_data)  # noqa: E731
+    else:
+        fn = {
+            "ours": lambda: moe_all2all.custom_kernel(data),
+            "torch": lambda: baseline_nccl.moe_torch(data),
+        }[impl]
     out = fn()
     expected = oracle.moe_expected_output(cfg, mine, world_size, emulate_reference_rounding=True)
     ok, msg = oracle.check_moe_output(out, expected)
@@ -156,12 +167,31 @@ def eval_moe_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, 
             layer.check(sync=True)
         except Exception as exc:  # noqa: BLE001
             res["ok"], res["msg"] = False, str(exc)
-    if mode == "benchmark" and device.type == "cuda":
-        times = timing.time_cuda(fn, warmup=warmup, iters=iters, flush=True, barrier=dist.barrier if world_size > 1 else None)
-        times = timing.max_over_ranks(times)
-        res["time_us"] = timing.summarize(times)["mean_ms"] * 1e3
-        res["median_us"] = timing.summarize(times)["median_ms"] * 1e3
+    if mode == "benchmark":
+        _benchmark(fn, device, world_size, warmup, iters, res)
     return res
+
+
+def _benchmark(fn, device: torch.device, world_size: int, warmup: int, iters: int, res: Dict[str, Any]) -> None:
+    """CUDA events on a GPU; wall clock around barrier-aligned calls on CPU ranks.  Max over ranks."""
+    barrier = dist.barrier if world_size > 1 else None
+    if device.type == "cuda":
+        times = timing.time_cuda(fn, warmup=warmup, iters=iters, flush=True, barrier=barrier)
+    else:
+        import time
+
+        for _ in range(warmup):
+            fn()
+        times = []
+        for _ in range(iters):
+            if barrier is not None:
+                barrier()
+            t0 = time.perf_counter()
+            fn()
+            times.append((time.perf_counter() - t0) * 1e3)
+    times = timing.max_over_ranks(times)
+    res["time_us"] = timing.summarize(times)["mean_ms"] * 1e3
+    res["median_us"] = timing.summarize(times)["median_ms"] * 1e3
 
 
 def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, mode: str,
@@ -177,10 +207,16 @@ def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: s
         for r in range(world_size)
     ]
     data = everyone[rank]
-    fn = {
-        "ours": lambda: gemm_rs.custom_kernel(data),
-        "torch": lambda: baseline_nccl.gemm_rs_torch(data),
-    }[impl]
+    if impl == "reference":
+        from . import reference_arm
+
+        ref = reference_arm.load_gemm_rs()
+        fn = lambda: ref.ref_kernel(data)  # noqa: E731
+    else:
+        fn = {
+            "ours": lambda: gemm_rs.custom_kernel(data),
+            "torch": lambda: baseline_nccl.gemm_rs_torch(data),
+        }[impl]
     out = fn()
     a_all, w_all = [d[0] for d in everyone], [d[1] for d in everyone]
     truth = oracle.gemm_rs_truth(a_all, w_all, data[2], rank, dtype=torch.float32 if device.type == "cuda" else torch.float64)
@@ -189,15 +225,18 @@ def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: s
     ok, msg = oracle.check_gemm_rs_output(out, oracle.gemm_rs_fused_rounding(a_all, w_all, data[2], rank))
     rel = oracle.relative_error(out, truth)
     res: Dict[str, Any] = {"spec": spec, "ok": bool(ok and rel < 1e-2), "msg": msg, "rel_err": rel}
-    if mode == "benchmark" and device.type == "cuda":
-        times = timing.time_cuda(fn, warmup=warmup, iters=iters, flush=True, barrier=dist.barrier if world_size > 1 else None)
-        times = timing.max_over_ranks(times)
-        res["time_us"] = timing.summarize(times)["mean_ms"] * 1e3
-        res["median_us"] = timing.summarize(times)["median_ms"] * 1e3
+    if mode == "benchmark":
+        _benchmark(fn, device, world_size, warmup, iters, res)
     return res
 
 
 def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup: int, iters: int) -> List[Dict[str, Any]]:
+    if task == "headline_cpu":
+        # the fp32 two-rank CPU configuration of configs/headline.yml (device: cpu)
+        specs = [dict(c) for c in contract.load_task("headline")["moe"] if c.get("device") == "cpu"]
+        for c in specs:
+            c["max_num_tokens"] = c["tokens_per_rank"]
+        return [eval_moe_shape(rank, world_size, c, impl, mode, warmup, iters) for c in specs]
     specs = contract.task_specs(task, "tests" if mode == "test" else "benchmarks")
     results = []
     for spec in specs:
@@ -236,9 +275,11 @@ def summarize_results(results: List[Dict[str, Any]]) -> Dict[str, Any]:
 
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--task", choices=["all2all", "gemm_rs"], required=True)
+    ap.add_argument("--task", choices=["all2all", "gemm_rs", "headline_cpu"], required=True)
     ap.add_argument("--mode", choices=["test", "benchmark"], default="test")
-    ap.add_argument("--impl", choices=["ours", "torch"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "torch", "reference"], default="ours",
+                    help="ours = this package; torch = vectorised torch.distributed restatement; "
+                         "reference = the unmodified reference files under baseline/_ref")
     ap.add_argument("--world-size", type=int, default=None)
     ap.add_argument("--backend", default=None)
     ap.add_argument("--warmup", type=int, default=3)
@@ -247,6 +288,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     args = ap.parse_args(argv)
 
     backend = args.backend or ("nccl" if torch.cuda.is_available() else "gloo")
+    if args.task == "headline_cpu":
+        backend = "gloo"
+        args.world_size = args.world_size or 2
     if "RANK" in os.environ:
         rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
         if backend == "nccl":

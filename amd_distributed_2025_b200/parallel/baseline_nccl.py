@@ -110,7 +110,15 @@ class TorchAllToAll:
         src_k = recv_meta[:, 3].to(torch.int64)
         w = weights[src_token, src_k].to(torch.float32)
         acc = out_tokens.to(torch.float32)
-        acc.index_add_(0, src_token, recv_rows.to(torch.float32) * w[:, None])
+        t, k = weights.shape
+        if recv_rows.shape[0] == t * k:
+            # every (token, k) entry came back exactly once: order the rows by (token, k) and
+            # sum over k in that fixed order (deterministic, and no scatter)
+            order = torch.argsort(src_token * k + src_k)
+            contrib = (recv_rows[order].to(torch.float32) * w[order][:, None]).view(t, k, -1)
+            acc[:t] += contrib.sum(dim=1)
+        else:
+            acc.index_add_(0, src_token, recv_rows.to(torch.float32) * w[:, None])
         out_tokens.copy_(acc)
         return out_tokens
 

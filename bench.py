@@ -27,7 +27,6 @@ Launch: ``python bench.py`` (one GPU) or
 from __future__ import annotations
 
 import argparse
-import importlib.util
 import json
 import os
 import socket
@@ -44,6 +43,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from amd_distributed_2025_b200 import contract  # noqa: E402
+from amd_distributed_2025_b200.harness import reference_arm  # noqa: E402
 from amd_distributed_2025_b200.utils import timing  # noqa: E402
 from amd_distributed_2025_b200.utils.clocks import ClockSampler  # noqa: E402
 
@@ -121,19 +121,6 @@ class Ours:
         self.gemm.release_ops()
 
 
-def _load_module(name: str, path: str, extra_path: str):
-    sys.modules.pop("task", None)
-    sys.path.insert(0, extra_path)
-    try:
-        spec = importlib.util.spec_from_file_location(name, path)
-        mod = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(mod)
-    finally:
-        sys.path.remove(extra_path)
-        sys.modules.pop("task", None)
-    return mod
-
-
 class Reference:
     """The reference's own code, unmodified, imported from baseline/_ref."""
 
@@ -142,17 +129,13 @@ class Reference:
 
     def __init__(self, rank: int, ws: int):
         self.rank, self.ws = rank, ws
-        self.a2a = _load_module("ref_all2all", os.path.join(REF_DIR, "all2all", "reference.py"),
-                                os.path.join(REF_DIR, "all2all"))
-        self.grs = _load_module("ref_gemm_rs", os.path.join(REF_DIR, "gemm-rs", "reference.py"),
-                                os.path.join(REF_DIR, "gemm-rs"))
+        self.a2a = reference_arm.load_all2all(REF_DIR)
+        self.grs = reference_arm.load_gemm_rs(REF_DIR)
 
     def _moe_tuple(self, item, x, indices, weights):
-        c = item["cfg"]
-        cfg = self.a2a.MoEConfig(c.num_experts, c.experts_per_token, c.hidden_dim, c.max_num_tokens, c.in_dtype, c.out_dtype)
-        d = object.__new__(self.a2a.RankTestData)
+        d = object.__new__(contract.RankTestData)
         d.num_tokens, d.x, d.indices, d.weights = item["data"].num_tokens, x, indices, weights
-        return cfg, d, self.rank, self.ws
+        return reference_arm.moe_tuple(self.a2a, item["cfg"], d, self.rank, self.ws)
 
     def call(self, item) -> torch.Tensor:
         if item["kind"] == "moe":
@@ -221,7 +204,7 @@ def main() -> int:
         if rank == 0:
             print(json.dumps({"error": f"--gpus {args.gpus} but WORLD_SIZE={ws}; launch with torch.distributed.run"}))
         return 2
-    if args.impl == "reference" and not os.path.exists(os.path.join(REF_DIR, "all2all", "reference.py")):
+    if args.impl == "reference" and not reference_arm.reference_available(REF_DIR):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no copy of the reference files"}))
         return 0
 

@@ -63,3 +63,29 @@ def test_gemm_rs_cpu_two_ranks_bias_counts_world_size_times():
         assert r["ok"], r["msg"]
         assert r["rel"] < 1e-2
         assert r["shape"] == [32, 48]
+
+
+def _reference_arm_rank(rank, world_size):
+    from amd_distributed_2025_b200.harness import reference_arm
+
+    ref = reference_arm.load_all2all()
+    cfg, mine, _, _ = contract.make_moe_inputs(16, 2, 64, 8, 5, rank, world_size, device="cpu", dtype=torch.float32,
+                                               fixed_num_tokens=8, weights="softmax")
+    y = ref.ref_kernel(reference_arm.moe_tuple(ref, cfg, mine, rank, world_size))
+    ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, mine, world_size))
+    grs = reference_arm.load_gemm_rs()
+    return {"ok": bool(ok), "msg": msg, "has_gemm": hasattr(grs, "ref_kernel") and hasattr(grs, "generate_input")}
+
+
+def test_unmodified_reference_files_load_and_agree_with_the_oracle():
+    """The comparison arm imports the reference's own files (when a copy is present) and its
+    result on CPU ranks equals the communication-free oracle."""
+    import pytest
+
+    from amd_distributed_2025_b200.harness import reference_arm
+
+    if not reference_arm.reference_available():
+        pytest.skip("no copy of the reference files under baseline/_ref")
+    for r in run_ranks(_reference_arm_rank, 2, "gloo", (), 300.0):
+        assert r["ok"], r["msg"]
+        assert r["has_gemm"]
