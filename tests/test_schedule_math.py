@@ -1,0 +1,70 @@
+"""CPU tests pinning the index arithmetic the kernels implement (slot assignment of dispatch,
+tile order and ownership of the fused GEMM)."""
+import itertools
+
+import pytest
+import torch
+
+from amd_distributed_2025_b200 import contract, oracle
+from amd_distributed_2025_b200.contract import MoEConfig, RankTestData
+from amd_distributed_2025_b200.ops import schedule_math as sm
+
+
+@pytest.mark.parametrize("ws,E,k,T", [(1, 8, 2, 5), (2, 16, 2, 32), (4, 64, 6, 8), (8, 256, 8, 16)])
+def test_dispatch_slots_reproduce_the_oracle_layout(ws, E, k, T):
+    cfg = MoEConfig(E, k, 8, T, torch.float32, torch.float32)
+    data = []
+    for r in range(ws):
+        g = torch.Generator().manual_seed(100 + r)
+        data.append(RankTestData(cfg, g, r, device="cpu", fixed_num_tokens=T if r % 2 == 0 else max(T - 3, 0)))
+    counts, routes = sm.dispatch_slots([d.indices.tolist() for d in data], E)
+    e_local = E // ws
+    for owner in range(ws):
+        n_tok, _, meta = oracle.moe_dispatch_oracle(cfg, data, owner)
+        # expert_num_tokens = column sums of the count matrix over the owner's experts
+        assert n_tok.tolist() == [sum(counts[s][owner * e_local + el] for s in range(ws)) for el in range(e_local)]
+        for el in range(e_local):
+            for slot in range(int(n_tok[el])):
+                e, src, t, kk = meta[el, slot, :4].tolist()
+                assert routes[src][(t, kk)] == (owner, el, slot)
+    # every slot of an expert is used exactly once
+    for owner in range(ws):
+        used = sorted((el, slot) for r in routes for (o, el, slot) in r.values() if o == owner)
+        assert len(used) == len(set(used))
+
+
+@pytest.mark.parametrize("m,n,ws,block_n,ctas,splits",
+                         [(8192, 8192, 8, 256, 2, 1), (8192, 8192, 1, 256, 2, 1), (2048, 5120, 8, 192, 2, 1),
+                          (256, 5120, 8, 128, 2, 1), (256, 5120, 1, 256, 2, 3), (64, 7168, 8, 256, 1, 4),
+                          (4096, 2880, 4, 256, 2, 1), (1000 // 8 * 8, 2880, 2, 128, 1, 1)])
+def test_gemm_tile_order_covers_everything_once_and_ends_with_own_rows(m, n, ws, block_n, ctas, splits):
+    m_tiles, n_tiles = -(-m // 128), -(-n // block_n)
+    m_groups = -(-m_tiles // ctas)
+    for rank in range(ws):
+        order = sm.gemm_tile_order(m, n, ws, rank, block_n, ctas, splits)
+        assert sorted(order) == sorted(itertools.product(range(m_groups), range(n_tiles), range(splits)))
+        # the row groups that hold this rank's rows are the last ones visited
+        rows = m // ws
+        own_groups = {b // ctas for b in range(m_tiles) if rank in sm.gemm_tile_owners(m, ws, b)
+                      and (rank * rows <= b * 128 or ws == 1 or rows < 128 * ctas)}
+        seq = [mg for mg, _, _ in order]
+        first_own = min(i for i, mg in enumerate(seq) if mg in own_groups)
+        if rows % (128 * ctas) == 0 and ws > 1:
+            assert all(mg in own_groups for mg in seq[first_own:])
+        # K slices of one tile are adjacent (they run concurrently on neighbouring schedulers)
+        for i in range(0, len(order), splits):
+            assert len({(mg, nb) for mg, nb, _ in order[i : i + splits]}) == 1
+
+
+def test_ownership_and_arrival_counts():
+    # 8 ranks x 1024 rows: blocks 0..7 are rank 0's, all of them wholly owned
+    assert sm.gemm_tile_owners(8192, 8, 0) == [0] and sm.gemm_tile_owners(8192, 8, 8) == [1]
+    assert sm.block_is_own(8192, 8, 1, 8) and not sm.block_is_own(8192, 8, 0, 8)
+    # 8 ranks x 32 rows: one 128-row block holds four owners, nobody owns it wholly
+    assert sm.gemm_tile_owners(256, 8, 1) == [4, 5, 6, 7]
+    assert not any(sm.block_is_own(256, 8, r, 1) for r in range(8))
+    # ragged end: M = 64 has half a block, a block past the end has no owner
+    assert sm.gemm_tile_owners(64, 8, 0) == list(range(8)) and sm.gemm_tile_owners(64, 8, 1) == []
+    assert sm.expected_arrivals(8, 1, fused_own=True) == 7
+    assert sm.expected_arrivals(8, 1, fused_own=False) == 8
+    assert sm.expected_arrivals(2, 3, fused_own=True) == 6  # K slices are always staged
