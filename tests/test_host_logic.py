@@ -112,3 +112,16 @@ def test_roofline_arithmetic():
     assert m["roofline_us"] == pytest.approx(2 * 896 * 14336 / 770e9 * 1e6)
     loaded = roofline.load_peaks()
     assert loaded["source"] in ("measured", "fallback") and loaded["hbm_gbs"] > 1000
+
+
+def test_roofline_report_for_a_bench_line():
+    line = {"n_gpus": 8, "per_config_us": {
+        "moe_decode": {"us": 140.0}, "gemm_rs_large": {"us": 480.0}, "gemm_rs_sweep_m256": {"us": 100.0}}}
+    peaks = {"hbm_gbs": 6500.0, "bf16_tflops": 1600.0, "bf16_tflops_sustained": 1400.0, "nvlink_gbs_per_dir": 770.0}
+    rep = roofline.report(line, peaks)
+    assert set(rep) == set(line["per_config_us"])
+    big = rep["gemm_rs_large"]
+    assert big["roofline_us"] == pytest.approx(2 * 8192 * 8192 * 3584 / 1400e12 * 1e6)
+    assert big["fraction_of_roofline"] == pytest.approx(big["roofline_us"] / 480.0)
+    # decode: about 7/8 of 1024 rows of 14 336 bytes leave every rank, once per phase
+    assert 25.0 < rep["moe_decode"]["roofline_us"] < 40.0
