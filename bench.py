@@ -208,6 +208,10 @@ def main() -> int:
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no copy of the reference files"}))
         return 0
 
+    if not torch.cuda.is_available():
+        if rank == 0:
+            print(json.dumps({"error": "no CUDA device: the headline benchmark runs on B200 GPUs only"}))
+        return 2
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if ws > 1 or args.impl == "reference":
