@@ -14,6 +14,7 @@
 
 #include "fp8_gemm.h"
 #include "gemm_rs.h"
+#include "host_ops.h"
 #include "host_shm_heap.h"
 #include "moe.h"
 #include "status.h"
@@ -289,6 +290,180 @@ void fp8_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& a_scal
   cuda_check(b200::launch_fp8_gemm(g, at::cuda::getCurrentCUDAStream()), "fp8_gemm launch");
 }
 
+// ---------------------------------------------------------------------------------------
+// CPU ranks over the shared-memory heap (host_ops.h)
+// ---------------------------------------------------------------------------------------
+
+b200::HostMoeLayout host_layout(const std::vector<int64_t>& offsets) {
+  TORCH_CHECK(offsets.size() == 4, "expected offsets of (counts, expert_x, expert_meta, expert_y)");
+  b200::HostMoeLayout lay;
+  lay.counts = (uint64_t)offsets[0];
+  lay.expert_x = (uint64_t)offsets[1];
+  lay.expert_meta = (uint64_t)offsets[2];
+  lay.expert_y = (uint64_t)offsets[3];
+  return lay;
+}
+
+b200::HostMoeShape host_shape(const b200::HostShmHeap& heap, int64_t num_experts, int64_t topk, int64_t hidden,
+                              int64_t max_recv, at::ScalarType in_dtype, at::ScalarType out_dtype) {
+  TORCH_CHECK(num_experts > 0 && num_experts % heap.world_size() == 0, "num_experts must divide by the world size");
+  TORCH_CHECK(topk > 0 && hidden > 0 && max_recv > 0, "bad MoE shape");
+  b200::HostMoeShape s;
+  s.num_experts = (int)num_experts;
+  s.topk = (int)topk;
+  s.hidden = (int)hidden;
+  s.max_recv = (int)max_recv;
+  s.in_dtype = dtype_code(in_dtype);
+  s.out_dtype = dtype_code(out_dtype);
+  return s;
+}
+
+void host_check_layout(const b200::HostShmHeap& heap, const b200::HostMoeLayout& lay, const b200::HostMoeShape& s) {
+  const uint64_t El = (uint64_t)s.num_experts / heap.world_size();
+  const uint64_t cells = El * (uint64_t)s.max_recv;
+  const uint64_t end_counts = lay.counts + (uint64_t)heap.world_size() * s.num_experts * 4;
+  const uint64_t end_x = lay.expert_x + cells * s.hidden * b200::host_dtype_bytes(s.in_dtype);
+  const uint64_t end_meta = lay.expert_meta + cells * 5 * 4;
+  const uint64_t end_y = lay.expert_y + cells * s.hidden * b200::host_dtype_bytes(s.out_dtype);
+  TORCH_CHECK(lay.counts >= b200::kHeapHeaderBytes && end_counts <= heap.bytes() && end_x <= heap.bytes() &&
+                  end_meta <= heap.bytes() && end_y <= heap.bytes(),
+              "MoE regions do not fit the shared-memory slab");
+}
+
+py::tuple host_moe_dispatch(b200::HostShmHeap& heap, std::vector<int64_t> offsets, const at::Tensor& x,
+                            const at::Tensor& indices, int64_t num_experts, int64_t max_recv,
+                            at::ScalarType out_dtype, int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(x.device().is_cpu() && indices.device().is_cpu(), "host_moe_dispatch takes CPU tensors");
+  TORCH_CHECK(x.dim() == 2 && indices.dim() == 2 && x.is_contiguous(), "x [tokens, hidden] contiguous, indices [tokens, k]");
+  TORCH_CHECK(indices.size(0) <= x.size(0), "more index rows than tokens");
+  const b200::HostMoeLayout lay = host_layout(offsets);
+  const b200::HostMoeShape s = host_shape(heap, num_experts, indices.size(1), x.size(1), max_recv, x.scalar_type(), out_dtype);
+  host_check_layout(heap, lay, s);
+  const at::Tensor idx = indices.to(at::kInt).contiguous();
+  const int num_tokens = (int)idx.size(0);
+  at::Tensor route = at::empty({(int64_t)num_tokens * s.topk, 3}, at::TensorOptions().dtype(at::kInt));
+  at::Tensor expert_num = at::empty({s.num_experts / heap.world_size()}, at::TensorOptions().dtype(at::kInt));
+  b200::StatusWord w;
+  {
+    py::gil_scoped_release release;
+    w = b200::host_moe_dispatch(heap, lay, s, x.data_ptr(), idx.data_ptr<int32_t>(), num_tokens,
+                                route.data_ptr<int32_t>(), expert_num.data_ptr<int32_t>(), (uint64_t)epoch,
+                                (uint64_t)timeout_ns);
+  }
+  return py::make_tuple(status_to_dict(w), route, expert_num);
+}
+
+at::Tensor host_region(b200::HostShmHeap& heap, uint64_t offset, std::vector<int64_t> shape, at::ScalarType dtype) {
+  return at::from_blob(heap.base(heap.rank()) + offset, shape, at::TensorOptions().dtype(dtype).device(at::kCPU));
+}
+
+void host_moe_expert_scale(b200::HostShmHeap& heap, std::vector<int64_t> offsets, int64_t num_experts, int64_t topk,
+                           int64_t hidden, int64_t max_recv, at::ScalarType in_dtype, at::ScalarType out_dtype,
+                           const at::Tensor& expert_num_tokens, double scale) {
+  const b200::HostMoeLayout lay = host_layout(offsets);
+  const b200::HostMoeShape s = host_shape(heap, num_experts, topk, hidden, max_recv, in_dtype, out_dtype);
+  host_check_layout(heap, lay, s);
+  const int64_t El = s.num_experts / heap.world_size();
+  TORCH_CHECK(expert_num_tokens.scalar_type() == at::kInt && expert_num_tokens.is_contiguous() &&
+                  expert_num_tokens.numel() == El,
+              "expert_num_tokens must be int32 [local experts]");
+  at::Tensor x = host_region(heap, lay.expert_x, {El, max_recv, hidden}, in_dtype);
+  at::Tensor y = host_region(heap, lay.expert_y, {El, max_recv, hidden}, out_dtype);
+  const int32_t* num = expert_num_tokens.data_ptr<int32_t>();
+  if (El * max_recv * hidden <= (1 << 18)) {
+    // small buffers: two calls over everything cost less than two per expert; rows past the
+    // counts hold stale values that nobody reads
+    y.copy_(x);
+    y.mul_(scale);
+    return;
+  }
+  for (int64_t el = 0; el < El; ++el) {
+    const int64_t rows = std::min<int64_t>(std::max<int32_t>(num[el], 0), max_recv);
+    if (rows == 0) continue;
+    // the reference converts to the output type first and multiplies in that type
+    // (all2all/reference.py:265)
+    at::Tensor ys = y.select(0, el).narrow(0, 0, rows);
+    ys.copy_(x.select(0, el).narrow(0, 0, rows));
+    ys.mul_(scale);
+  }
+}
+
+py::dict host_moe_combine(b200::HostShmHeap& heap, std::vector<int64_t> offsets, int64_t num_experts, int64_t max_recv,
+                          at::ScalarType in_dtype, const at::Tensor& route, const at::Tensor& weights, at::Tensor out,
+                          int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(out.device().is_cpu() && out.dim() == 2 && out.is_contiguous(), "out [tokens, hidden] contiguous on CPU");
+  TORCH_CHECK(weights.dim() == 2 && weights.scalar_type() == at::kFloat && weights.is_contiguous(),
+              "weights must be float32 [tokens, k] contiguous");
+  const int num_tokens = (int)weights.size(0);
+  TORCH_CHECK(out.size(0) >= num_tokens, "out has fewer rows than weights");
+  TORCH_CHECK(route.scalar_type() == at::kInt && route.is_contiguous() && route.dim() == 2 && route.size(1) == 3 &&
+                  route.size(0) == (int64_t)num_tokens * weights.size(1),
+              "route must be the int32 [tokens * k, 3] table returned by dispatch");
+  const b200::HostMoeLayout lay = host_layout(offsets);
+  const b200::HostMoeShape s = host_shape(heap, num_experts, weights.size(1), out.size(1), max_recv, in_dtype, out.scalar_type());
+  host_check_layout(heap, lay, s);
+  // a route table is only as good as its producer: owners, experts and slots must be in range
+  {
+    const int32_t* r = route.data_ptr<int32_t>();
+    const int El = s.num_experts / heap.world_size();
+    for (int64_t i = 0; i < route.size(0); ++i) {
+      TORCH_CHECK(r[3 * i] < heap.world_size() && (r[3 * i] < 0 || (r[3 * i + 1] >= 0 && r[3 * i + 1] < El &&
+                                                                   r[3 * i + 2] >= 0 && r[3 * i + 2] < s.max_recv)),
+                  "route entry ", i, " is out of range");
+    }
+  }
+  at::Tensor rows = at::empty({(int64_t)num_tokens, (int64_t)s.topk, (int64_t)s.hidden}, out.options());
+  b200::StatusWord w;
+  {
+    py::gil_scoped_release release;
+    w = b200::host_moe_pull(heap, lay, s, route.data_ptr<int32_t>(), num_tokens, rows.data_ptr(), (uint64_t)epoch,
+                            (uint64_t)timeout_ns);
+  }
+  if (w.code == b200::STATUS_OK && num_tokens > 0) {
+    // fp32 accumulator, k ascending, one rounding
+    at::Tensor acc = at::zeros({(int64_t)num_tokens, (int64_t)s.hidden}, out.options().dtype(at::kFloat));
+    for (int64_t j = 0; j < s.topk; ++j) {
+      acc.addcmul_(rows.select(1, j).to(at::kFloat), weights.select(1, j).unsqueeze(1));
+    }
+    out.narrow(0, 0, num_tokens).copy_(acc);
+  }
+  return status_to_dict(w);
+}
+
+py::tuple host_reduce_scatter(b200::HostShmHeap& heap, int64_t stage_offset, int64_t stage_bytes, const at::Tensor& partial,
+                              const c10::optional<at::Tensor>& bias_once, int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(partial.device().is_cpu() && partial.dim() == 2 && partial.is_contiguous(), "partial [M, N] contiguous on CPU");
+  const int ws = heap.world_size();
+  const int64_t m = partial.size(0), n = partial.size(1);
+  TORCH_CHECK(m % ws == 0, "M must divide by the world size");
+  const int dt = dtype_code(partial.scalar_type());
+  const int64_t need = m * n * b200::host_dtype_bytes(dt);  // world * (M / world) * N elements
+  TORCH_CHECK(need <= stage_bytes, "staging region of ", stage_bytes, " bytes is smaller than the ", need, " needed");
+  TORCH_CHECK(stage_offset >= (int64_t)b200::kHeapHeaderBytes && (uint64_t)(stage_offset + stage_bytes) <= heap.bytes(),
+              "staging region outside the slab");
+  at::Tensor bias_f32;
+  if (bias_once.has_value() && bias_once->defined()) {
+    TORCH_CHECK(bias_once->numel() == n, "bias must have N elements");
+    bias_f32 = bias_once->to(at::kFloat).contiguous();
+  }
+  b200::StatusWord w;
+  {
+    py::gil_scoped_release release;
+    w = b200::host_rs_exchange(heap, (uint64_t)stage_offset, partial.data_ptr(), (int)m, (int)n,
+                               b200::host_dtype_bytes(dt), (uint64_t)epoch, (uint64_t)timeout_ns);
+  }
+  const int64_t rows = m / ws;
+  if (w.code != b200::STATUS_OK) return py::make_tuple(status_to_dict(w), at::empty({rows, n}, partial.options()));
+  // fp32 sum in rank order, one rounding
+  at::Tensor stage = host_region(heap, (uint64_t)stage_offset, {ws, rows, n}, partial.scalar_type());
+  at::Tensor acc = at::zeros({rows, n}, partial.options().dtype(at::kFloat));
+  for (int src = 0; src < ws; ++src) {
+    acc.add_(src == heap.rank() ? partial.narrow(0, src * rows, rows) : stage.select(0, src));
+  }
+  if (bias_f32.defined()) acc.add_(bias_f32);
+  return py::make_tuple(status_to_dict(w), acc.to(partial.scalar_type()));
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -344,14 +519,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("prefix"), py::arg("rank"), py::arg("world_size"), py::arg("bytes"))
       .def("open_peers", [](b200::HostShmHeap& h, int64_t timeout_ns) { return h.open_peers((uint64_t)timeout_ns); })
       .def("close", &b200::HostShmHeap::close)
+      .def("unlink", &b200::HostShmHeap::unlink)
       .def("signal", [](b200::HostShmHeap& h, int row, int dst, int64_t epoch) { h.signal(row, dst, (uint64_t)epoch); })
       .def("wait",
-           [](b200::HostShmHeap& h, int row, int src, int64_t epoch, int64_t timeout_ns) {
+           [](b200::HostShmHeap& h, int row, int src, int64_t epoch, int64_t timeout_ns, int phase) {
              py::gil_scoped_release release;
-             b200::StatusWord w = h.wait(row, src, (uint64_t)epoch, (uint64_t)timeout_ns, b200::PHASE_TEST);
+             b200::StatusWord w = h.wait(row, src, (uint64_t)epoch, (uint64_t)timeout_ns, (uint32_t)phase);
              py::gil_scoped_acquire acquire;
              return status_to_dict(w);
-           })
+           },
+           py::arg("row"), py::arg("src"), py::arg("epoch"), py::arg("timeout_ns"), py::arg("phase") = (int)b200::PHASE_TEST)
       .def("barrier",
            [](b200::HostShmHeap& h, int64_t epoch, int64_t timeout_ns) {
              py::gil_scoped_release release;
@@ -375,6 +552,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   m.attr("FLAG_BARRIER") = (int)b200::FLAG_BARRIER;
   m.attr("FLAG_TEST") = (int)b200::FLAG_TEST;
+  m.def("host_moe_dispatch", &host_moe_dispatch);
+  m.def("host_moe_expert_scale", &host_moe_expert_scale);
+  m.def("host_moe_combine", &host_moe_combine);
+  m.def("host_reduce_scatter", &host_reduce_scatter);
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_expert_scale", &moe_expert_scale);
   m.def("moe_combine", &moe_combine);

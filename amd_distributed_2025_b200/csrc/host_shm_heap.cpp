@@ -48,7 +48,9 @@ HostShmHeap::HostShmHeap(const std::string& prefix, int rank, int world_size, ui
   ::close(fd);
   if (p == MAP_FAILED) throw std::runtime_error("HostShmHeap: mmap failed");
   base_[rank_] = static_cast<uint8_t*>(p);
-  std::memset(base_[rank_], 0, bytes_);
+  // The segment was created exclusively just above, so every page is zero-filled by the kernel.
+  // It is NOT cleared here: a peer may map it as soon as it has its full size and could already
+  // have stored a flag that a late memset would wipe out.
 }
 
 HostShmHeap::~HostShmHeap() { close(); }
@@ -87,6 +89,10 @@ void HostShmHeap::close() {
   }
   if (!prefix_.empty()) shm_unlink(seg_name(prefix_, rank_).c_str());
   prefix_.clear();
+}
+
+void HostShmHeap::unlink() {
+  if (!prefix_.empty()) shm_unlink(seg_name(prefix_, rank_).c_str());
 }
 
 void HostShmHeap::signal(int row, int dst, uint64_t epoch) {

@@ -18,7 +18,7 @@ namespace b200 {
 
 class HostShmHeap {
  public:
-  // Creates (and zeroes) this rank's slab "/<prefix>_<rank>" of `bytes` (>= header).
+  // Creates this rank's slab "/<prefix>_<rank>" of `bytes` (>= header); a fresh segment is all zero.
   HostShmHeap(const std::string& prefix, int rank, int world_size, uint64_t bytes);
   ~HostShmHeap();
   HostShmHeap(const HostShmHeap&) = delete;
@@ -27,6 +27,10 @@ class HostShmHeap {
   // Maps the peers' slabs, waiting up to timeout_ns for them to appear.  Returns false on timeout.
   bool open_peers(uint64_t timeout_ns);
   void close();
+  // Removes the slab's name; mappings stay valid.  Once every rank has mapped every slab (a
+  // barrier after open_peers) the names are no longer needed, and a rank that is killed
+  // later leaves nothing behind in /dev/shm.
+  void unlink();
 
   int rank() const { return rank_; }
   int world_size() const { return world_; }

@@ -236,7 +236,9 @@ def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup
         specs = [dict(c) for c in contract.load_task("headline")["moe"] if c.get("device") == "cpu"]
         for c in specs:
             c["max_num_tokens"] = c["tokens_per_rank"]
-        return [eval_moe_shape(rank, world_size, c, impl, mode, warmup, iters) for c in specs]
+        results = [eval_moe_shape(rank, world_size, c, impl, mode, warmup, iters) for c in specs]
+        release_workspaces()
+        return results
     specs = contract.task_specs(task, "tests" if mode == "test" else "benchmarks")
     results = []
     for spec in specs:
@@ -256,12 +258,13 @@ def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup
 
 def release_workspaces() -> None:
     """Collective, orderly teardown of every cached symmetric workspace of this process."""
-    from ..models import gemm_rs, moe_all2all
+    from ..models import gemm_rs, host_ops, moe_all2all
 
     if torch.cuda.is_available():
         torch.cuda.synchronize()
     moe_all2all.release_layers()
     gemm_rs.release_ops()
+    host_ops.release()  # every rank holds its own mappings of the shared-memory slabs: no meeting needed
 
 
 def summarize_results(results: List[Dict[str, Any]]) -> Dict[str, Any]:

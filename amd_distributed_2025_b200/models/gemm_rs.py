@@ -199,9 +199,23 @@ def release_ops() -> None:
     _OPS.clear()
 
 
+def _cpu_ranks_share_a_node() -> bool:
+    from ..parallel.host_symm import single_node
+
+    return single_node()
+
+
 def custom_kernel(data: GemmRsInput, bias_mode: str = "per_rank", backend: str = "auto") -> torch.Tensor:
-    """``[M/ws, N]`` bf16 result of the row-parallel linear layer (gemm-rs/reference.py:36-60)."""
+    """``[M/ws, N]`` bf16 result of the row-parallel linear layer (gemm-rs/reference.py:36-60).
+
+    ``backend``: "auto" = the fused kernel for CUDA tensors, the shared-memory operator
+    (models/host_ops.py) for CPU tensors when all ranks share a machine, library collectives
+    otherwise; "shm" and "torch" force the latter two."""
     a, w, bias = data
+    if backend == "shm" or (backend == "auto" and not a.is_cuda and _cpu_ranks_share_a_node()):
+        from . import host_ops
+
+        return host_ops.gemm_rs_custom_kernel(data, bias_mode)
     if backend == "torch" or (backend == "auto" and not a.is_cuda):
         if bias_mode == "once" and bias is not None and dist.is_initialized():
             out = gemm_rs_torch((a, w, None))

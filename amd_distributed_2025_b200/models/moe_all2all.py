@@ -245,11 +245,25 @@ def release_layers() -> None:
     _LAYERS.clear()
 
 
+def _cpu_ranks_share_a_node() -> bool:
+    from ..parallel.host_symm import single_node
+
+    return single_node()
+
+
 def custom_kernel(data: MoEInput, backend: str = "auto") -> torch.Tensor:
     """Dispatch -> ``* (1 + rank)`` -> combine; returns ``y[num_tokens, hidden]`` in
-    ``cfg.out_dtype`` on the rank's device (all2all/reference.py:256-272)."""
+    ``cfg.out_dtype`` on the rank's device (all2all/reference.py:256-272).
+
+    ``backend``: "auto" = the fused kernels for CUDA tensors, the shared-memory operators
+    (models/host_ops.py) for CPU tensors when all ranks share a machine, library collectives
+    otherwise; "shm" and "torch" force the latter two."""
     cfg, rank_data, rank, world_size = data
     x = rank_data.x
+    if backend == "shm" or (backend == "auto" and not x.is_cuda and _cpu_ranks_share_a_node()):
+        from . import host_ops
+
+        return host_ops.moe_custom_kernel(data)
     if backend == "torch" or (backend == "auto" and not x.is_cuda):
         ata = TorchAllToAll(cfg, rank, world_size)
         n_tok, ex, em = ata.dispatch(x, rank_data.indices)

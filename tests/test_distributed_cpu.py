@@ -18,7 +18,7 @@ def _moe_rank(rank, world_size, spec):
         for r in range(world_size)
     ]
     cfg, mine, _, _ = everyone[rank]
-    y = moe_all2all.custom_kernel((cfg, mine, rank, world_size))
+    y = moe_all2all.custom_kernel((cfg, mine, rank, world_size), backend="torch")
     want = oracle.moe_expected_output(cfg, mine, world_size)
     ok, msg = oracle.check_moe_output(y, want)
     rel = oracle.relative_error(y, oracle.moe_expected_output(cfg, mine, world_size))
@@ -52,7 +52,7 @@ def _gemm_rank(rank, world_size, m, n, k, has_bias):
     from amd_distributed_2025_b200.models import gemm_rs
 
     everyone = [contract.make_gemm_rs_inputs(r, world_size, m, n, k, has_bias, 5, device="cpu") for r in range(world_size)]
-    out = gemm_rs.custom_kernel(everyone[rank])
+    out = gemm_rs.custom_kernel(everyone[rank], backend="torch")
     truth = oracle.gemm_rs_truth([e[0] for e in everyone], [e[1] for e in everyone], everyone[rank][2], rank)
     ok, msg = oracle.check_gemm_rs_output(out, truth.to(out.dtype))
     return {"ok": bool(ok), "msg": msg, "rel": oracle.relative_error(out, truth), "shape": list(out.shape)}

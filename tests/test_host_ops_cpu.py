@@ -1,0 +1,152 @@
+"""CPU ranks over shared memory: the one-sided protocols of the two operators under real
+concurrency (2 to 8 processes), against the communication-free oracle."""
+import multiprocessing as mp
+import os
+import time
+
+import pytest
+import torch
+
+from amd_distributed_2025_b200 import contract, oracle
+from amd_distributed_2025_b200.harness.eval import run_ranks
+
+CPU = torch.device("cpu")
+
+
+def _moe_inputs(spec, seed, world_size):
+    return [
+        contract.make_moe_inputs(spec["E"], spec["k"], spec["H"], spec["T"], seed, r, world_size, device=CPU,
+                                 dtype=getattr(torch, spec["dtype"]), fixed_num_tokens=spec.get("fixed"),
+                                 routing=spec.get("routing", "uniform"), weights=spec.get("weights", "softmax"))
+        for r in range(world_size)
+    ]
+
+
+def _moe_rank(rank, world_size, spec, calls):
+    from amd_distributed_2025_b200.models import host_ops, moe_all2all
+
+    res = {"ok": True, "msg": "", "layout_ok": True, "layout_msg": "", "rel": 0.0}
+    for call in range(calls):
+        # same configuration, new tokens and routing every call: the buffers are reused with
+        # nothing but the protocol's flags between the calls
+        everyone = _moe_inputs(spec, spec["seed"] + 17 * call, world_size)
+        cfg, mine, _, _ = everyone[rank]
+        y = moe_all2all.custom_kernel((cfg, mine, rank, world_size))  # CPU tensors, one node -> shared memory
+        layer = host_ops.get_layer(cfg, rank, world_size)
+        exact = oracle.moe_expected_output(cfg, mine, world_size)
+        ok, msg = oracle.check_moe_output(y, exact)
+        lay_ok, lay_msg = oracle.compare_dispatch_layout(
+            (layer.expert_num_tokens, layer.expert_x, layer.expert_meta),
+            oracle.moe_dispatch_oracle(cfg, [e[1] for e in everyone], rank),
+        )
+        res["ok"] &= bool(ok) and list(y.shape) == [mine.num_tokens, cfg.hidden_dim] and y.dtype == cfg.out_dtype
+        res["msg"] = res["msg"] or msg
+        res["layout_ok"] &= bool(lay_ok)
+        res["layout_msg"] = res["layout_msg"] or lay_msg
+        res["rel"] = max(res["rel"], oracle.relative_error(y, exact))
+    res["cached_layers"] = len(host_ops._LAYERS)
+    host_ops.release()
+    return res
+
+
+@pytest.mark.parametrize(
+    "world_size,spec,rel",
+    [
+        (2, dict(E=16, k=2, H=256, T=32, seed=11, dtype="float32", fixed=32), 1e-6),
+        (4, dict(E=8, k=2, H=64, T=4, seed=1236, dtype="float16", weights="rand"), 2e-3),  # random token counts
+        (8, dict(E=64, k=6, H=512, T=48, seed=5, dtype="bfloat16", routing="zipf"), 1e-2),
+    ],
+)
+def test_moe_over_shared_memory_matches_the_oracle_call_after_call(world_size, spec, rel):
+    for r in run_ranks(_moe_rank, world_size, "gloo", (spec, 3), 300.0):
+        assert r["ok"], r["msg"]
+        assert r["layout_ok"], r["layout_msg"]  # reference row order: source rank, then (token, k)
+        assert r["rel"] < rel
+        assert r["cached_layers"] == 1
+
+
+def _gemm_rank(rank, world_size, m, n, k, calls):
+    from amd_distributed_2025_b200.models import gemm_rs, host_ops
+
+    res = {"ok": True, "msg": "", "rel": 0.0, "once_ok": True}
+    for call in range(calls):
+        everyone = [contract.make_gemm_rs_inputs(r, world_size, m, n, k, True, 5 + call, device=CPU) for r in range(world_size)]
+        a_all, w_all, bias = [e[0] for e in everyone], [e[1] for e in everyone], everyone[rank][2]
+        out = gemm_rs.custom_kernel(everyone[rank])  # bias on every rank, as the reference does
+        ok, msg = oracle.check_gemm_rs_output(out, oracle.gemm_rs_fused_rounding(a_all, w_all, bias, rank))
+        res["ok"] &= bool(ok) and list(out.shape) == [m // world_size, n]
+        res["msg"] = res["msg"] or msg
+        res["rel"] = max(res["rel"], oracle.relative_error(out, oracle.gemm_rs_truth(a_all, w_all, bias, rank)))
+        once = gemm_rs.custom_kernel(everyone[rank], bias_mode="once")
+        no_bias = oracle.gemm_rs_truth(a_all, w_all, None, rank)
+        res["once_ok"] &= oracle.relative_error(once, no_bias + bias.to(no_bias.dtype)) < 1e-2
+    host_ops.release()
+    return res
+
+
+@pytest.mark.parametrize("world_size,m,n,k", [(2, 64, 48, 256), (4, 128, 96, 512), (8, 64, 40, 1024)])
+def test_gemm_rs_over_shared_memory_alternates_parities_without_barriers(world_size, m, n, k):
+    # 3 calls x 2 bias modes = 6 operator calls in a row on the same two staging parities
+    for r in run_ranks(_gemm_rank, world_size, "gloo", (m, n, k, 3), 300.0):
+        assert r["ok"], r["msg"]
+        assert r["rel"] < 1e-2
+        assert r["once_ok"]
+
+
+def _backends_agree(rank, world_size):
+    from amd_distributed_2025_b200.models import moe_all2all
+
+    cfg, mine, _, _ = contract.make_moe_inputs(16, 4, 128, 16, 3, rank, world_size, device=CPU, dtype=torch.float32,
+                                               fixed_num_tokens=16, weights="softmax")
+    data = (cfg, mine, rank, world_size)
+    a = moe_all2all.custom_kernel(data, backend="shm")
+    b = moe_all2all.custom_kernel(data, backend="torch")
+    return {"max_diff": float((a - b).abs().max())}
+
+
+def test_shared_memory_and_library_collective_backends_agree():
+    for r in run_ranks(_backends_agree, 2, "gloo", (), 300.0):
+        assert r["max_diff"] < 1e-5
+
+
+# -- failure detection: a rank that stops calling ------------------------------------------
+
+def _leaver(prefix, rank, world_size, q):
+    from amd_distributed_2025_b200.contract import MoEConfig
+    from amd_distributed_2025_b200.models.host_ops import HostMoEAllToAll
+    from amd_distributed_2025_b200.utils.status import StatusError
+
+    torch.set_num_threads(1)
+    cfg = MoEConfig(num_experts=9, experts_per_token=2, hidden_dim=32, max_num_tokens=8, in_dtype=torch.float32,
+                    out_dtype=torch.float32)
+    layer = HostMoEAllToAll(cfg, rank, world_size, prefix=prefix, wait_limit_ms=300.0)
+    gen = torch.Generator().manual_seed(rank)
+    x = torch.randn(8, 32, generator=gen)
+    idx = torch.stack([torch.randperm(9, generator=gen)[:2] for _ in range(8)]).to(torch.int32)
+    w = torch.full((8, 2), 0.5)
+    layer.forward(x, idx, w, 1.0)  # step 1: everybody takes part
+    if rank == world_size - 1:
+        q.put((rank, "left", None, None, 0.0))  # leaves between steps, nothing in flight
+        return
+    t0 = time.perf_counter()
+    try:
+        layer.forward(x, idx, w, 1.0)
+        q.put((rank, "no error", None, None, time.perf_counter() - t0))
+    except StatusError as exc:
+        q.put((rank, exc.code, exc.phase, exc.status["peer"], time.perf_counter() - t0))
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_others_wait_with_a_status():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    prefix = f"b200_test_leave_{os.getpid()}"
+    procs = [ctx.Process(target=_leaver, args=(prefix, r, 3, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert got[2][1] == "left"
+    for rank, code, phase, peer, seconds in got[:2]:
+        assert (code, phase, peer) == ("timeout", "moe_counts", 2)
+        assert 0.25 < seconds < 10.0  # gave up after the limit, not much later
