@@ -19,7 +19,6 @@ import torch.distributed as dist
 
 from ..contract import META_DIM, GemmRsInput, MoEConfig, MoEInput
 from ..parallel.host_symm import HostSymmetricWorkspace, shared_prefix
-from ..parallel.symm_mem import SlabLayout
 from .gemm_rs import gemm_rs_slab_layout
 from .moe_all2all import moe_slab_layout
 

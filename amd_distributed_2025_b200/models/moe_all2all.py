@@ -23,7 +23,6 @@ from __future__ import annotations
 from typing import Dict, Optional, Tuple
 
 import torch
-import torch.distributed as dist
 
 from ..contract import META_DIM, MoEConfig, MoEInput
 from ..parallel.baseline_nccl import TorchAllToAll

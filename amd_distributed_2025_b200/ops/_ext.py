@@ -16,7 +16,7 @@ import importlib.util
 import os
 import sys
 import threading
-from typing import List, Optional
+from typing import List
 
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC_DIR = os.path.join(_PKG_DIR, "csrc")

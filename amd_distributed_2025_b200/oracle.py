@@ -24,7 +24,7 @@ Facts encoded here (and pinned by unit tests):
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 

@@ -18,8 +18,6 @@ the reference's.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
-
 import torch
 import torch.distributed as dist
 

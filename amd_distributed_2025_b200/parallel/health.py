@@ -14,7 +14,6 @@ from __future__ import annotations
 import time
 from typing import Callable, Dict, List, Optional
 
-import torch.distributed as dist
 
 
 class PeerLostError(RuntimeError):

@@ -33,7 +33,7 @@ import socket
 import statistics
 import sys
 import time
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Tuple
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
