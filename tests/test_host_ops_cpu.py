@@ -159,3 +159,17 @@ def test_a_rank_that_leaves_between_steps_ends_the_others_wait_with_a_status():
     for rank, code, phase, peer, seconds in got[:2]:
         assert (code, phase, peer) == ("timeout", "moe_counts", 2)
         assert 0.25 < seconds < 10.0  # gave up after the limit, not much later
+
+
+def test_single_process_world_of_one_needs_no_process_group():
+    from amd_distributed_2025_b200.models import gemm_rs, host_ops, moe_all2all
+
+    cfg, d, _, _ = contract.make_moe_inputs(8, 2, 64, 16, 1, 0, 1, device=CPU, dtype=torch.float32)
+    y = moe_all2all.custom_kernel((cfg, d, 0, 1))
+    ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, d, 1))
+    assert ok, msg
+    a, w, b = contract.make_gemm_rs_inputs(0, 1, 32, 48, 64, True, 3, device=CPU)
+    out = gemm_rs.custom_kernel((a, w, b))
+    ok, msg = oracle.check_gemm_rs_output(out, oracle.gemm_rs_fused_rounding([a], [w], b, 0))
+    assert ok, msg
+    host_ops.release()
