@@ -125,3 +125,22 @@ def test_roofline_report_for_a_bench_line():
     assert big["fraction_of_roofline"] == pytest.approx(big["roofline_us"] / 480.0)
     # decode: about 7/8 of 1024 rows of 14 336 bytes leave every rank, once per phase
     assert 25.0 < rep["moe_decode"]["roofline_us"] < 40.0
+
+
+def test_report_table_has_ratios_geomeans_and_the_speed_of_light_column():
+    from amd_distributed_2025_b200.harness import report
+
+    specs = contract.task_specs("gemm_rs", "benchmarks")[:2]
+    by_arm = {
+        "ours": [{"spec": specs[0], "ok": True, "time_us": 50.0}, {"spec": specs[1], "ok": True, "time_us": 200.0}],
+        "torch": [{"spec": specs[0], "ok": True, "time_us": 100.0}, {"spec": specs[1], "ok": False, "time_us": 800.0}],
+    }
+    text = report.render("gemm_rs", 8, by_arm)
+    rows = [r for r in text.splitlines() if r.startswith("|")]
+    assert len(rows) == 2 + 2 + 1  # header, rule, two shapes, geometric mean
+    assert "2.00x" in rows[2] and "4.00x" in rows[3]
+    assert "FAILS: torch" in rows[3] and "passes" in rows[2]
+    assert "**100.0**" in rows[4] and "**282.8**" in rows[4] and "2.83x" in rows[4]
+    sol = report.speed_of_light("gemm_rs")
+    assert len(sol) >= 6 and all(v > 0 for v in sol.values())
+    assert f"{sol[report._shape_key('gemm_rs', specs[0])]:.2f}" in rows[2]
