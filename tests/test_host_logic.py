@@ -144,3 +144,56 @@ def test_report_table_has_ratios_geomeans_and_the_speed_of_light_column():
     sol = report.speed_of_light("gemm_rs")
     assert len(sol) >= 6 and all(v > 0 for v in sol.values())
     assert f"{sol[report._shape_key('gemm_rs', specs[0])]:.2f}" in rows[2]
+
+
+def test_clock_sampler_only_reads_and_summarises_the_samples_under_load(monkeypatch):
+    """Against a fake NVML: the sampler calls getters only, takes the median SM clock of the
+    samples under load and decodes the throttle reasons seen there."""
+    import sys
+    import time
+    import types
+
+    from amd_distributed_2025_b200.utils.clocks import ClockSampler
+
+    calls = []
+    script = [(1965, 200_000, 0x0), (1305, 990_000, 0x4), (1290, 1_000_000, 0x4), (1320, 980_000, 0x4 | 0x20)]
+    state = {"i": 0}
+
+    class FakeNvml(types.ModuleType):
+        NVML_CLOCK_SM = 1
+
+        def __getattr__(self, name):  # anything that is not one of the getters below: refuse
+            raise AssertionError(f"the sampler touched {name}")
+
+    fake = FakeNvml("pynvml")
+    fake.nvmlInit = lambda: calls.append("init")
+    fake.nvmlShutdown = lambda: calls.append("shutdown")
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("handle", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965
+
+    def cur():
+        return script[min(state["i"], len(script) - 1)]
+
+    fake.nvmlDeviceGetClockInfo = lambda h, kind: cur()[0]
+    fake.nvmlDeviceGetPowerUsage = lambda h: cur()[1]
+
+    def reasons(h):
+        mask = cur()[2]
+        state["i"] += 1
+        return mask
+
+    fake.nvmlDeviceGetCurrentClocksEventReasons = reasons
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+
+    s = ClockSampler(0, interval_s=0.001)
+    s.start()
+    deadline = time.time() + 5.0
+    while state["i"] < len(script) + 2 and time.time() < deadline:
+        time.sleep(0.002)
+    out = s.stop()
+    assert calls[0] == "init" and calls[-1] == "shutdown"
+    assert out["sm_max_mhz"] == 1965
+    assert 1290 <= out["sm_mhz"] <= 1320  # the idle 1965 MHz sample is not "under load"
+    assert out["power_w_max"] == 1000.0
+    assert out["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
+    assert out["samples_under_load"] < out["samples"]
