@@ -195,6 +195,201 @@ void moe_forward(SymmHeap& heap, const at::Tensor& x, const at::Tensor& indices,
   moe_combine(heap, out, weights, route, x.size(0), max_recv, off_expert_y, combine_epoch, timeout_ns);
 }
 
+
+// ----------------------------------------------------- MoE, de-duplicating protocol ----
+// One object per layer keeps everything that does not change between calls (heap, offsets,
+// scratch, grid sizes, epochs), so a call converts three or four tensors and launches.
+class MoeDedupEngine {
+ public:
+  MoeDedupEngine(std::shared_ptr<SymmHeap> heap, int64_t num_experts, int64_t topk, int64_t hidden, int64_t max_tokens,
+                 int64_t max_recv, at::ScalarType dtype, bool partial_fp32, std::vector<int64_t> offsets,
+                 at::Tensor expert_y, at::Tensor blk_hist, at::Tensor route, at::Tensor expert_num_tokens,
+                 int64_t timeout_ns)
+      : heap_(std::move(heap)), E_(num_experts), k_(topk), H_(hidden), max_tokens_(max_tokens), max_recv_(max_recv),
+        dtype_(dtype), partial_fp32_(partial_fp32), expert_y_(std::move(expert_y)), blk_hist_(std::move(blk_hist)),
+        route_(std::move(route)), expert_num_tokens_(std::move(expert_num_tokens)), timeout_ns_(timeout_ns) {
+    TORCH_CHECK(heap_->peers_open(), "symmetric heap: peers are not mapped yet");
+    const int ws = heap_->world_size();
+    TORCH_CHECK(E_ > 0 && E_ % ws == 0, "num_experts must be divisible by world_size");
+    TORCH_CHECK(k_ >= 1 && k_ <= 32, "experts_per_token must be in 1..32");
+    TORCH_CHECK(offsets.size() == 9, "expected 9 region offsets");
+    El_ = E_ / ws;
+    TORCH_CHECK(El_ * max_recv_ < (1ll << 31), "expert buffer has too many rows for 32-bit row ids");
+    lay_.off_counts = (uint64_t)offsets[0];
+    lay_.off_expert_x = (uint64_t)offsets[1];
+    lay_.off_expert_meta = (uint64_t)offsets[2];
+    lay_.off_expert_y = (uint64_t)offsets[3];
+    lay_.off_land = (uint64_t)offsets[4];
+    lay_.off_tok_rows = (uint64_t)offsets[5];
+    lay_.off_tok_w = (uint64_t)offsets[6];
+    lay_.off_tok_mark = (uint64_t)offsets[7];
+    lay_.off_ret = (uint64_t)offsets[8];
+    elem_ = (int64_t)c10::elementSize(dtype_);
+    dtype_code_ = dtype_code(dtype_);
+    TORCH_CHECK(route_.scalar_type() == at::kInt && route_.is_contiguous() && route_.numel() >= 2 * max_tokens_ * k_,
+                "route must hold 2 int32 per (token, k) entry");
+    TORCH_CHECK(expert_num_tokens_.scalar_type() == at::kInt && expert_num_tokens_.numel() >= El_, "expert_num_tokens too small");
+    TORCH_CHECK(expert_y_.is_contiguous() && expert_y_.scalar_type() == dtype_ && expert_y_.numel() == El_ * max_recv_ * H_,
+                "expert_y must be a contiguous [E_local, max_recv, hidden] tensor of the layer's dtype");
+    c10::cuda::CUDAGuard guard(heap_->device());
+    combine_blocks_ = b200::moe_dedup_combine_max_blocks(heap_->device());
+    TORCH_CHECK(blk_hist_.scalar_type() == at::kInt && blk_hist_.is_contiguous(), "blk_hist must be contiguous int32");
+  }
+
+  int64_t dispatch_epoch() const { return dispatch_epoch_; }
+  int64_t combine_epoch() const { return combine_epoch_; }
+  void set_timeout_ns(int64_t t) { timeout_ns_ = t; }
+  void set_trace(const c10::optional<at::Tensor>& dispatch_trace, const c10::optional<at::Tensor>& combine_trace) {
+    trace_d_ = check_trace(dispatch_trace);
+    trace_c_ = check_trace(combine_trace);
+  }
+
+  void dispatch(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
+                bool fuse_scale, double scale) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == dtype_ && x.size(1) == H_,
+                "x must be a contiguous [T, hidden] CUDA tensor of the layer's dtype");
+    TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() && indices.scalar_type() == at::kInt &&
+                    indices.size(0) == x.size(0) && indices.size(1) == k_,
+                "indices must be a contiguous [T, k] int32 CUDA tensor");
+    TORCH_CHECK(x.get_device() == heap_->device(), "x is not on the heap's device");
+    const int64_t T = x.size(0);
+    TORCH_CHECK(T <= max_tokens_, T, " tokens exceed max_num_tokens=", max_tokens_);
+    const float* wptr = nullptr;
+    if (weights.has_value() && weights->defined()) {
+      TORCH_CHECK(weights->is_cuda() && weights->scalar_type() == at::kFloat && weights->is_contiguous() &&
+                      weights->dim() == 2 && weights->size(0) == T && weights->size(1) == k_,
+                  "weights must be contiguous fp32 [T, k]");
+      wptr = weights->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(heap_->device());
+    const int ws = heap_->world_size();
+    const int n = (int)(T * k_);
+    const int max_blocks = b200::moe_dedup_dispatch_max_blocks(heap_->device(), (int)E_, n);
+    TORCH_CHECK(blk_hist_.numel() >= (int64_t)max_blocks * E_, "blk_hist scratch too small");
+    b200::MoeDedupDispatchParams p;
+    p.x = x.data_ptr();
+    p.indices = indices.data_ptr<int32_t>();
+    p.weights = wptr;
+    p.num_tokens = (int32_t)T;
+    p.k = (int32_t)k_;
+    p.num_experts = (int32_t)E_;
+    p.num_local_experts = (int32_t)El_;
+    p.world_size = ws;
+    p.rank = heap_->rank();
+    p.max_recv = (int32_t)max_recv_;
+    p.max_tokens = (int32_t)max_tokens_;
+    p.dtype = dtype_code_;
+    p.row_bytes = (uint32_t)(H_ * elem_);
+    p.pieces = pieces_for((int)T, max_blocks);
+    p.fuse_scale = fuse_scale ? 1 : 0;
+    p.scale = (float)scale;
+    p.epoch = (uint64_t)(++dispatch_epoch_);
+    p.timeout_ns = (uint64_t)timeout_ns_;
+    fill_peer_bases(*heap_, p.peer_base);
+    p.layout = lay_;
+    p.expert_y = expert_y_.data_ptr();
+    p.blk_hist = blk_hist_.data_ptr<int32_t>();
+    p.route = reinterpret_cast<int2*>(route_.data_ptr<int32_t>());
+    p.expert_num_tokens = expert_num_tokens_.data_ptr<int32_t>();
+    p.sync_counters = heap_->sync_counters();
+    p.status = heap_->status_device();
+    p.trace = trace_d_;
+    // enough warps for every (source, token, piece) of the replication pass, never more CTAs than fit at once
+    const int64_t want = ((int64_t)ws * std::max<int64_t>(T, 1) * p.pieces + 7) / 8;
+    const int grid = (int)std::max<int64_t>(std::min<int64_t>(max_blocks, want), 1);
+    weights_sent_ = wptr != nullptr;
+    num_tokens_ = (int)T;
+    cuda_check(b200::launch_moe_dedup_dispatch(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dedup_dispatch launch");
+  }
+
+  void combine(at::Tensor out, const at::Tensor& weights, const c10::optional<at::Tensor>& expert_y) {
+    const int64_t T = num_tokens_;
+    TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.is_contiguous() && out.scalar_type() == dtype_ &&
+                    out.size(0) >= T && out.size(1) == H_,
+                "out must be a contiguous [>= T, hidden] CUDA tensor of the layer's dtype");
+    TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == at::kFloat && weights.is_contiguous() && weights.dim() == 2 &&
+                    weights.size(0) >= T && weights.size(1) == k_,
+                "weights must be contiguous fp32 [T, k]");
+    const void* ey = expert_y_.data_ptr();
+    if (expert_y.has_value() && expert_y->defined()) {
+      TORCH_CHECK(expert_y->is_cuda() && expert_y->is_contiguous() && expert_y->scalar_type() == dtype_ &&
+                      expert_y->numel() == El_ * max_recv_ * H_,
+                  "expert_y does not have the dispatch layout / dtype");
+      ey = expert_y->data_ptr();
+    }
+    c10::cuda::CUDAGuard guard(heap_->device());
+    const int ws = heap_->world_size();
+    b200::MoeDedupCombineParams p;
+    p.out = out.data_ptr();
+    p.weights = weights.data_ptr<float>();
+    p.route = reinterpret_cast<const int2*>(route_.data_ptr<int32_t>());
+    p.expert_y = ey;
+    p.num_tokens = (int32_t)T;
+    p.k = (int32_t)k_;
+    p.hidden = (int32_t)H_;
+    p.num_local_experts = (int32_t)El_;
+    p.world_size = ws;
+    p.rank = heap_->rank();
+    p.max_recv = (int32_t)max_recv_;
+    p.max_tokens = (int32_t)max_tokens_;
+    p.dtype = dtype_code_;
+    p.partial_fp32 = partial_fp32_ ? 1 : 0;
+    p.weights_sent = weights_sent_ ? 1 : 0;
+    p.pieces = pieces_for((int)T, combine_blocks_);
+    p.epoch = (uint64_t)(++combine_epoch_);
+    p.dispatch_epoch = (uint64_t)dispatch_epoch_;
+    p.timeout_ns = (uint64_t)timeout_ns_;
+    fill_peer_bases(*heap_, p.peer_base);
+    p.layout = lay_;
+    p.sync_counters = heap_->sync_counters();
+    p.status = heap_->status_device();
+    p.trace = trace_c_;
+    const int64_t want = ((int64_t)ws * std::max<int64_t>(T, 1) * p.pieces + 7) / 8;
+    const int grid = (int)std::max<int64_t>(std::min<int64_t>(combine_blocks_, want), 1);
+    cuda_check(b200::launch_moe_dedup_combine(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dedup_combine launch");
+  }
+
+  // dispatch (carrying the weights, applying expert_y = expert_x * scale on the way) + combine
+  void forward(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& weights, at::Tensor out, double scale) {
+    dispatch(x, indices, weights, true, scale);
+    combine(out, weights, c10::nullopt);
+  }
+
+ private:
+  uint64_t* check_trace(const c10::optional<at::Tensor>& t) {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() && t->numel() >= 8,
+                "trace must be a contiguous int64 CUDA tensor with at least 8 elements");
+    keep_.push_back(*t);
+    return reinterpret_cast<uint64_t*>(t->data_ptr<int64_t>());
+  }
+  // A row is split over several warps when there are fewer tokens than warps (decode).
+  int pieces_for(int tokens, int blocks) const {
+    const int64_t row_bytes = H_ * elem_;
+    if (row_bytes % 16 != 0) return 1;
+    const int nv = (int)(row_bytes / 16);
+    int pcs = (blocks * 8) / std::max(tokens * heap_->world_size(), 1);
+    pcs = std::min(pcs, std::max(nv / 64, 1));  // at least 1 KiB per piece
+    return std::max(1, std::min(pcs, 8));
+  }
+
+  std::shared_ptr<SymmHeap> heap_;
+  int64_t E_, k_, H_, max_tokens_, max_recv_, El_ = 0, elem_ = 2;
+  at::ScalarType dtype_;
+  int dtype_code_ = 0;
+  bool partial_fp32_;
+  b200::MoeDedupLayout lay_;
+  at::Tensor expert_y_, blk_hist_, route_, expert_num_tokens_;
+  int64_t timeout_ns_;
+  int64_t dispatch_epoch_ = 0, combine_epoch_ = 0;
+  int combine_blocks_ = 1;
+  bool weights_sent_ = false;
+  int num_tokens_ = 0;
+  uint64_t* trace_d_ = nullptr;
+  uint64_t* trace_c_ = nullptr;
+  std::vector<at::Tensor> keep_;
+};
+
 // ------------------------------------------------------------------------- GEMM-RS ----
 
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
@@ -549,6 +744,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              return at::from_blob(h.base(r) + offset, shape, at::TensorOptions().dtype(dtype).device(at::kCPU));
            },
            py::arg("rank"), py::arg("offset"), py::arg("shape"), py::arg("dtype"));
+
+  py::class_<MoeDedupEngine, std::shared_ptr<MoeDedupEngine>>(m, "MoeDedupEngine")
+      .def(py::init<std::shared_ptr<SymmHeap>, int64_t, int64_t, int64_t, int64_t, int64_t, at::ScalarType, bool,
+                    std::vector<int64_t>, at::Tensor, at::Tensor, at::Tensor, at::Tensor, int64_t>(),
+           py::arg("heap"), py::arg("num_experts"), py::arg("topk"), py::arg("hidden"), py::arg("max_tokens"),
+           py::arg("max_recv"), py::arg("dtype"), py::arg("partial_fp32"), py::arg("offsets"), py::arg("expert_y"),
+           py::arg("blk_hist"), py::arg("route"), py::arg("expert_num_tokens"), py::arg("timeout_ns"))
+      .def("dispatch", &MoeDedupEngine::dispatch, py::arg("x"), py::arg("indices"), py::arg("weights") = py::none(),
+           py::arg("fuse_scale") = false, py::arg("scale") = 1.0)
+      .def("combine", &MoeDedupEngine::combine, py::arg("out"), py::arg("weights"), py::arg("expert_y") = py::none())
+      .def("forward", &MoeDedupEngine::forward)
+      .def("set_trace", &MoeDedupEngine::set_trace, py::arg("dispatch_trace") = py::none(), py::arg("combine_trace") = py::none())
+      .def("set_timeout_ns", &MoeDedupEngine::set_timeout_ns)
+      .def_property_readonly("dispatch_epoch", &MoeDedupEngine::dispatch_epoch)
+      .def_property_readonly("combine_epoch", &MoeDedupEngine::combine_epoch);
+  m.def("moe_dedup_dispatch_max_blocks", [](int device, int num_experts, int num_entries) {
+    c10::cuda::CUDAGuard guard(device);
+    return b200::moe_dedup_dispatch_max_blocks(device, num_experts, num_entries);
+  });
 
   m.attr("FLAG_BARRIER") = (int)b200::FLAG_BARRIER;
   m.attr("FLAG_TEST") = (int)b200::FLAG_TEST;

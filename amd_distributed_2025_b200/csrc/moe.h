@@ -73,4 +73,75 @@ cudaError_t launch_moe_expert_scale(const void* expert_x, void* expert_y, const 
 
 cudaError_t launch_moe_combine(const MoeCombineParams& p, cudaStream_t stream);
 
+// ---------------------------------------------------------------------------------------
+// De-duplicating protocol ("dedup" mode, the default)
+// ---------------------------------------------------------------------------------------
+// The reference sends one row per (token, k) entry in both directions
+// (all2all/reference.py:79-86,107-112; all2all/hipv8.py:80-97,144-161).  Here a token's
+// row crosses NVLink once per DESTINATION RANK: the sender stores it into a landing
+// buffer on the owner, indexed by (source rank, token), together with the final row
+// index of each of the token's entries on that owner.  The owner then replicates the
+// landed row into expert_x[e_local, slot] with local copies, so the dispatch layouts
+// stay those of the reference.  On the way back the owner forms, per (source, token),
+// the weighted sum over its local experts in fp32 and pushes that ONE row into the
+// source's return buffer; the source adds the rows of the owners it used.
+struct MoeDedupLayout {
+  uint64_t off_counts;       // int32 [world][num_experts]; row s is written by rank s
+  uint64_t off_expert_x;     // dtype [E_local][max_recv][hidden]
+  uint64_t off_expert_meta;  // int32 [E_local][max_recv][5]
+  uint64_t off_expert_y;     // dtype [E_local][max_recv][hidden]
+  uint64_t off_land;         // dtype [world][max_tokens][hidden]: row (s, t) = token t of rank s
+  uint64_t off_tok_rows;     // int32 [world][max_tokens][k]: final row of entry k on this rank, or -1
+  uint64_t off_tok_w;        // float [world][max_tokens][k]: routing weight of that entry
+  uint64_t off_tok_mark;     // uint32 [world][max_tokens]: low word of the dispatch epoch that landed (s, t)
+  uint64_t off_ret;          // dtype or float [world][max_tokens][hidden]: row (d, t) = owner d's partial of my token t
+};
+
+struct MoeDedupDispatchParams {
+  const void* x;             // [T, hidden]
+  const int32_t* indices;    // [T, k]
+  const float* weights;      // [T, k] or nullptr (then combine sends them)
+  int32_t num_tokens, k, num_experts, num_local_experts, world_size, rank, max_recv, max_tokens;
+  int32_t dtype;             // 0 = fp16, 1 = bf16, 2 = fp32
+  uint32_t row_bytes;
+  int32_t pieces;            // a row is moved by this many warps (small problems)
+  int32_t fuse_scale;        // 1: the replication pass also writes expert_y = expert_x * scale
+  float scale;
+  uint64_t epoch, timeout_ns;
+  uint64_t peer_base[kMaxWorldSize];
+  MoeDedupLayout layout;
+  void* expert_y;            // where the fused expert op writes (this rank's buffer)
+  int32_t* blk_hist;         // [grid][num_experts] (large kernel only)
+  int2* route;               // [T*k] (owner rank, row) or (-1, -1)
+  int32_t* expert_num_tokens;
+  uint32_t* sync_counters;   // [0] grid barrier, [1] finished CTAs
+  StatusBlock* status;
+  uint64_t* trace;           // optional [8] globaltimer stamps of CTA 0: start, counted, rows issued,
+                             // counts arrived, metadata stored, all sources delivered, replicated, (max) exit
+};
+
+struct MoeDedupCombineParams {
+  void* out;                 // [T, hidden]
+  const float* weights;      // [T, k]
+  const int2* route;         // from dispatch
+  const void* expert_y;      // this rank's expert outputs, dispatch layout (any local tensor)
+  int32_t num_tokens, k, hidden, num_local_experts, world_size, rank, max_recv, max_tokens;
+  int32_t dtype;
+  int32_t partial_fp32;      // return rows travel as fp32 instead of dtype
+  int32_t weights_sent;      // dispatch already delivered the weights
+  int32_t pieces;
+  uint64_t epoch, dispatch_epoch, timeout_ns;
+  uint64_t peer_base[kMaxWorldSize];
+  MoeDedupLayout layout;
+  uint32_t* sync_counters;   // [2] weights pushed, [3] partial rows pushed
+  StatusBlock* status;
+  uint64_t* trace;           // optional [8]: start, weights exchanged, partials pushed, all partials arrived, (max) exit
+};
+
+// Co-resident grid sizes (cooperative launches) for the current device.
+int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries);
+int moe_dedup_combine_max_blocks(int device);
+cudaError_t launch_moe_dedup_dispatch(const MoeDedupDispatchParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_moe_dedup_combine(const MoeDedupCombineParams& p, int grid, cudaStream_t stream);
+
 }  // namespace b200

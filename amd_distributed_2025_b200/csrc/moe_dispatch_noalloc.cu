@@ -82,7 +82,6 @@ extern "C" int b200_moe_dispatch_noalloc(const void* x, const int32_t* indices, 
       if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
       st->base = static_cast<unsigned char*>(ptr);
     }
-    epoch = ++st->epoch;
   }
   if (st->sms > B200_NOALLOC_MAX_SMS)
     return fail(-7, "b200_moe_dispatch_noalloc: device has more SMs than the scratch array was sized for");
@@ -97,6 +96,11 @@ extern "C" int b200_moe_dispatch_noalloc(const void* x, const int32_t* indices, 
   int grid = max_blocks;
   const long long want = std::max<long long>(std::max<long long>(count_blocks, (n + 7) / 8), 1);
   if (want < grid) grid = (int)want;
+  {
+    // every argument check has passed: only now does the call take a call number
+    std::lock_guard<std::mutex> lock(g_mutex);
+    epoch = ++st->epoch;
+  }
 
   unsigned char* base = st->base;
   // Words that must start at zero: barrier counters and the status block.  Flags and the

@@ -27,6 +27,13 @@
 //   * The array keeps what the previous call left.  Each call clears, on the given
 //     stream, the words that must start at zero (barrier counters, status); flags are
 //     compared against a call number that only grows, so old values are harmless.
+//   * An entry whose expert id is outside [0, num_experts), or whose slot would not fit
+//     max_recv, is dropped: its route is (-1, -1), the other entries are served and
+//     b200_moe_dispatch_noalloc_status() reports 2.
+//   * Call numbers are handed out under a lock in the order the host threads get there; two
+//     host threads that call concurrently may launch in the opposite order, which the flag
+//     comparison tolerates only if their kernels do not overlap -- one more reason to
+//     serialise callers.  Kernel waits are bounded at 2 seconds.
 //   * Nothing here calls cudaMalloc, cudaFree, cudaHostAlloc or any torch allocator.
 #pragma once
 #include <cuda_runtime.h>

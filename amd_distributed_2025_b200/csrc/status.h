@@ -27,6 +27,8 @@ enum Phase : uint32_t {
   PHASE_GEMM_PIPELINE = 6,   // an mbarrier of the GEMM pipeline
   PHASE_BARRIER = 7,         // stand-alone cross-GPU barrier
   PHASE_TEST = 8,            // wait used by the timeout self-test
+  PHASE_MOE_WEIGHTS = 9,     // waiting for the sources' routing weights (combine without a fused dispatch)
+  PHASE_MOE_RETURN = 10,     // waiting for the owners' pre-reduced return rows
 };
 
 struct StatusWord {
@@ -57,6 +59,7 @@ enum FlagRow : int {
   FLAG_MOE_Y_READY = 3,
   FLAG_RS_DONE = 4,
   FLAG_TEST = 5,
+  FLAG_MOE_RET = 6,
   FLAG_ROWS = 8,
 };
 

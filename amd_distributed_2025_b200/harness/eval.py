@@ -3,8 +3,9 @@
 The reference names an evaluator (``eval.py``) and helpers that are not part of its tree
 (all2all/task.yml:6-8, gemm-rs/task.yml:6-8); this module supplies that role.  For every
 shape it builds the inputs on every rank (``generate_input``), calls the entry point under
-test, checks the result with the task's tolerance against the communication-free oracle,
-and in benchmark mode times it with CUDA events, maximum over ranks, and ranks the run by
+test, checks the result with the task's tolerance against the communication-free oracle
+and, in test mode on GPUs, also with the reference's own unmodified ``check_implementation``
+(loaded from ``baseline/_ref``, run collectively on all ranks), and in benchmark mode times it with CUDA events, maximum over ranks, and ranks the run by
 the geometric mean over shapes (all2all/task.yml:68, gemm-rs/task.yml:62).
 
 Usage::
@@ -138,8 +139,40 @@ def moe_rank_data(spec: Dict[str, Any], rank: int, world_size: int, device: torc
     )
 
 
+_REFERENCE_MODULES: Dict[str, Any] = {}
+
+
+def _reference_module(task: str):
+    from . import reference_arm
+
+    if task not in _REFERENCE_MODULES:
+        _REFERENCE_MODULES[task] = reference_arm.load_all2all() if task == "all2all" else reference_arm.load_gemm_rs()
+    return _REFERENCE_MODULES[task]
+
+
+def reference_arm_data(cfg, mine, rank: int, world_size: int):
+    from . import reference_arm
+
+    return reference_arm.moe_tuple(_reference_module("all2all"), cfg, mine, rank, world_size)
+
+
+def _literal_check(task: str, data, out) -> tuple:
+    """``check_implementation(data, out)`` of the unmodified reference file (collective)."""
+    ok, msg = _reference_module(task).check_implementation(data, out)
+    return bool(ok), str(msg)
+
+
+def literal_check_possible(device: torch.device, world_size: int) -> bool:
+    """The reference's checker runs its oracle over ``torch.distributed`` on ``cuda:{rank}``
+    tensors, so it needs GPUs, an initialised process group and the reference files."""
+    from . import reference_arm
+
+    return (device.type == "cuda" and dist.is_available() and dist.is_initialized()
+            and dist.get_world_size() == world_size and reference_arm.reference_available())
+
+
 def eval_moe_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, mode: str,
-                   warmup: int = 3, iters: int = 10) -> Dict[str, Any]:
+                   warmup: int = 3, iters: int = 10, literal_check: bool = False) -> Dict[str, Any]:
     from ..models import moe_all2all
     from ..parallel import baseline_nccl
 
@@ -161,6 +194,13 @@ def eval_moe_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, 
     expected = oracle.moe_expected_output(cfg, mine, world_size, emulate_reference_rounding=True)
     ok, msg = oracle.check_moe_output(out, expected)
     res: Dict[str, Any] = {"spec": spec, "ok": bool(ok), "msg": msg, "num_tokens": mine.num_tokens}
+    if literal_check and impl != "reference":
+        # The task's own acceptance test, unmodified: it re-runs the reference's collective
+        # oracle on these inputs, so every rank calls it together (all2all/reference.py:275-283).
+        lit_ok, lit_msg = _literal_check("all2all", reference_arm_data(cfg, mine, rank, world_size), out)
+        res["literal_ok"] = bool(lit_ok)
+        if not lit_ok:
+            res["ok"], res["msg"] = False, "reference check_implementation: " + lit_msg[:300]
     if impl == "ours" and device.type == "cuda":
         layer = moe_all2all.get_layer(cfg, rank, world_size)
         try:
@@ -195,7 +235,7 @@ def _benchmark(fn, device: torch.device, world_size: int, warmup: int, iters: in
 
 
 def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: str, mode: str,
-                       warmup: int = 3, iters: int = 10) -> Dict[str, Any]:
+                       warmup: int = 3, iters: int = 10, literal_check: bool = False) -> Dict[str, Any]:
     from ..models import gemm_rs
     from ..parallel import baseline_nccl
 
@@ -225,6 +265,13 @@ def eval_gemm_rs_shape(rank: int, world_size: int, spec: Dict[str, Any], impl: s
     ok, msg = oracle.check_gemm_rs_output(out, oracle.gemm_rs_fused_rounding(a_all, w_all, data[2], rank))
     rel = oracle.relative_error(out, truth)
     res: Dict[str, Any] = {"spec": spec, "ok": bool(ok and rel < 1e-2), "msg": msg, "rel_err": rel}
+    if literal_check and impl != "reference" and dist_kind == "reference":
+        # gemm-rs/reference.py:63-71, unmodified and collective; meaningful as an acceptance
+        # gate only with the task's own operand distribution (see oracle.outlier_fraction)
+        lit_ok, lit_msg = _literal_check("gemm_rs", data, out)
+        res["literal_ok"] = bool(lit_ok)
+        if not lit_ok:
+            res["ok"], res["msg"] = False, "reference check_implementation: " + lit_msg[:300]
     if mode == "benchmark":
         _benchmark(fn, device, world_size, warmup, iters, res)
     return res
@@ -240,6 +287,7 @@ def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup
         release_workspaces()
         return results
     specs = contract.task_specs(task, "tests" if mode == "test" else "benchmarks")
+    literal = mode == "test" and impl == "ours" and literal_check_possible(_device_for(rank), world_size)
     results = []
     for spec in specs:
         spec = dict(spec)
@@ -247,11 +295,11 @@ def run_task(rank: int, world_size: int, task: str, mode: str, impl: str, warmup
         if task == "all2all":
             if spec["num_experts"] % world_size:
                 continue
-            results.append(eval_moe_shape(rank, world_size, spec, impl, mode, warmup, iters))
+            results.append(eval_moe_shape(rank, world_size, spec, impl, mode, warmup, iters, literal))
         else:
             if spec["m"] % world_size or spec["k"] % world_size:
                 continue
-            results.append(eval_gemm_rs_shape(rank, world_size, spec, impl, mode, warmup, iters))
+            results.append(eval_gemm_rs_shape(rank, world_size, spec, impl, mode, warmup, iters, literal))
     release_workspaces()
     return results
 
@@ -314,6 +362,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         line = {k: v for k, v in r.items() if k != "msg" or v}
         print(json.dumps(line))
     summary = summarize_results(results)
+    summary["literal_checker"] = sum(1 for r in results if r.get("literal_ok")) if any("literal_ok" in r for r in results) else None
     print(json.dumps({"task": args.task, "mode": args.mode, "impl": args.impl, "world_size": ws, **summary}))
     if args.json:
         with open(args.json, "w", encoding="utf-8") as fh:

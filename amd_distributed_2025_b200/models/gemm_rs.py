@@ -23,11 +23,11 @@ import torch.distributed as dist
 
 from ..contract import GemmRsInput
 from ..parallel.baseline_nccl import gemm_rs_torch
-from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace
+from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace, checked, checked_guard_bytes
 
 
-def gemm_rs_slab_layout(stage_bytes: int, counter_bytes: int, header_bytes: int) -> SlabLayout:
-    lay = SlabLayout(header_bytes)
+def gemm_rs_slab_layout(stage_bytes: int, counter_bytes: int, header_bytes: int, guard_bytes: int = 0) -> SlabLayout:
+    lay = SlabLayout(header_bytes, guard_bytes=guard_bytes)
     lay.add("counters0", counter_bytes)
     lay.add("counters1", counter_bytes)
     lay.add("stage0", stage_bytes)
@@ -52,6 +52,7 @@ class GemmRS:
         group=None,
         device: Optional[torch.device] = None,
         wait_limit_ms: Optional[float] = None,
+        monitor=None,
     ):
         from ..ops import _ext
 
@@ -61,7 +62,10 @@ class GemmRS:
         self.rank = rank if rank is not None else (dist.get_rank(group) if initialized else 0)
         self.stage_bytes, self.counter_bytes = int(stage_bytes), int(counter_bytes)
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        layout = gemm_rs_slab_layout(self.stage_bytes, self.counter_bytes, self.ext.HEAP_HEADER_BYTES)
+        layout = gemm_rs_slab_layout(self.stage_bytes, self.counter_bytes, self.ext.HEAP_HEADER_BYTES,
+                                     checked_guard_bytes())
+        # The arrival counters are plain counts, not call numbers: after an expired wait the
+        # workspace is poisoned until recover() zeroes both parities on every rank.
         self.ws = SymmetricWorkspace(
             layout,
             rank=self.rank,
@@ -69,7 +73,10 @@ class GemmRS:
             group=group,
             device=self.device,
             wait_limit_ms=wait_limit_ms,
+            poison_on_timeout=True,
         )
+        self.monitor = monitor  # optional parallel.health.HealthMonitor: peers are checked before every launch
+        self.checked = checked()
         self._plans: Dict[tuple, dict] = {}
         self._fits = set()  # problem sizes already known to fit this workspace
         self.max_ctas = 0  # 0 = one CTA per SM
@@ -111,6 +118,9 @@ class GemmRS:
         if bias_mode not in ("per_rank", "once"):
             raise ValueError("bias_mode must be 'per_rank' or 'once'")
         self.ws.check()
+        if self.monitor is not None:
+            self.monitor.beat()
+            self.monitor.assert_all_alive()
         if out is None:
             out = torch.empty((m // self.world_size, n), dtype=torch.bfloat16, device=a.device)
         epoch = self.ws.next_epoch("gemm_rs")
@@ -150,6 +160,12 @@ class GemmRS:
 
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
+        self.ws.check_canaries()
+
+    def recover(self) -> None:
+        """Collective: make the workspace usable again after an expired wait (both parities of
+        the arrival counters zeroed on every rank, call numbers restarted)."""
+        self.ws.recover(("counters0", "counters1"))
 
     def close(self, collective: bool = False) -> None:
         self.ws.close(collective)

@@ -9,10 +9,21 @@ all2all/reference.py:55-272):
 * ``custom_kernel((cfg, rank_data, rank, world_size)) -> y[num_tokens, hidden]``.
 
 Differences in mechanism, not in results: the three returned tensors are views of this
-rank's symmetric workspace that the *senders* filled directly (csrc/moe_kernels.cu), in
-the reference's row order (source rank, token, k); combine pulls expert outputs from the
-owners' workspaces using the route table that dispatch recorded, so no metadata or
-counts travel back.  Nothing in a call synchronises with the host.
+rank's symmetric workspace, in the reference's row order (source rank, token, k), and
+nothing in a call synchronises with the host.  Two protocols fill them (``mode``, default
+from ``B200_MOE_MODE``):
+
+* ``"dedup"`` (default, csrc/moe_dedup.cu): a token crosses NVLink once per destination
+  *rank*; the owner replicates the landed row into ``expert_x[e_local, slot]`` locally.
+  Combine runs on the owner: per (source, token) it forms the weighted sum over its local
+  experts in fp32 and pushes that one row back; the source adds the rows of the owners it
+  used.  ``partial_dtype=torch.float32`` makes those rows travel un-rounded.
+* ``"direct"`` (csrc/moe_kernels.cu): one row per (token, k) entry, stored by the sender
+  straight into the owner's ``expert_x``; combine pulls ``expert_y`` rows from the owners
+  with the route table that dispatch recorded.
+
+Calls alternate ``dispatch`` and ``combine`` (or use ``forward``); every rank issues the
+same sequence.
 
 On CPU tensors (or ``backend="torch"``) the layer falls back to the library-collective
 implementation in ``parallel/baseline_nccl.py``; that is how the fp32 two-rank CPU
@@ -20,27 +31,47 @@ configuration runs.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
 
 from ..contract import META_DIM, MoEConfig, MoEInput
 from ..parallel.baseline_nccl import TorchAllToAll
-from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace
+from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace, checked_guard_bytes
 
 _DTYPE_SIZE = {torch.float16: 2, torch.bfloat16: 2, torch.float32: 4}
 
 
-def moe_slab_layout(cfg: MoEConfig, world_size: int, header_bytes: int) -> SlabLayout:
-    """Offsets of the MoE regions inside every rank's slab."""
+MODES = ("dedup", "direct")
+
+
+def default_mode() -> str:
+    mode = os.environ.get("B200_MOE_MODE", "dedup").strip().lower()
+    if mode not in MODES:
+        raise ValueError(f"B200_MOE_MODE={mode!r}: expected one of {MODES}")
+    return mode
+
+
+def moe_slab_layout(cfg: MoEConfig, world_size: int, header_bytes: int, mode: str = "direct",
+                    partial_bytes: int = 0, guard_bytes: int = 0) -> SlabLayout:
+    """Offsets of the MoE regions inside every rank's slab.  The "dedup" protocol adds the
+    landing buffer, the per-(source, token) row lists / weights / marks and the return buffer."""
     e_local = cfg.num_local_experts(world_size)
     max_recv = cfg.max_recv(world_size)
     rows = e_local * max_recv
-    lay = SlabLayout(header_bytes)
+    lay = SlabLayout(header_bytes, guard_bytes=guard_bytes)
     lay.add("counts", world_size * cfg.num_experts * 4)
     lay.add("expert_meta", rows * META_DIM * 4)
     lay.add("expert_x", rows * cfg.hidden_dim * _DTYPE_SIZE[cfg.in_dtype])
     lay.add("expert_y", rows * cfg.hidden_dim * _DTYPE_SIZE[cfg.out_dtype])
+    if mode == "dedup":
+        toks = world_size * cfg.max_num_tokens
+        lay.add("land", toks * cfg.hidden_dim * _DTYPE_SIZE[cfg.in_dtype])
+        lay.add("tok_rows", toks * cfg.experts_per_token * 4)
+        lay.add("tok_w", toks * cfg.experts_per_token * 4)
+        lay.add("tok_mark", toks * 4)
+        lay.add("ret", toks * cfg.hidden_dim * (partial_bytes or _DTYPE_SIZE[cfg.out_dtype]))
     return lay
 
 
@@ -55,9 +86,25 @@ class MoEAllToAll:
         group=None,
         device: Optional[torch.device] = None,
         wait_limit_ms: Optional[float] = None,
+        mode: Optional[str] = None,
+        partial_dtype: Optional[torch.dtype] = None,
+        monitor=None,
     ):
         if cfg.in_dtype not in _DTYPE_SIZE or cfg.out_dtype not in _DTYPE_SIZE:
             raise ValueError("in_dtype / out_dtype must be float16, bfloat16 or float32")
+        if cfg.in_dtype != cfg.out_dtype:
+            # the reference converts with expert_x.to(out_dtype) (all2all/reference.py:262); its generator
+            # only ever produces equal types, and the device kernels move rows as bytes
+            raise ValueError(f"in_dtype {cfg.in_dtype} != out_dtype {cfg.out_dtype}: the GPU layer needs equal types")
+        self.mode = mode or default_mode()
+        if self.mode not in MODES:
+            raise ValueError(f"mode {self.mode!r}: expected one of {MODES}")
+        if partial_dtype not in (None, cfg.out_dtype, torch.float32):
+            raise ValueError("partial_dtype must be the output type or float32")
+        self.partial_fp32 = partial_dtype == torch.float32 and cfg.out_dtype != torch.float32
+        if cfg.experts_per_token > 32 and self.mode == "dedup":
+            raise ValueError("the dedup protocol handles at most 32 experts per token")
+        self.monitor = monitor  # optional parallel.health.HealthMonitor: peers are checked before every launch
         self.cfg = cfg
         self.rank = rank
         self.world_size = world_size
@@ -70,7 +117,8 @@ class MoEAllToAll:
 
         ext = _ext.load()
         self.ext = ext
-        layout = moe_slab_layout(cfg, world_size, ext.HEAP_HEADER_BYTES)
+        layout = moe_slab_layout(cfg, world_size, ext.HEAP_HEADER_BYTES, self.mode,
+                                 4 if self.partial_fp32 else 0, guard_bytes=checked_guard_bytes())
         self.ws = SymmetricWorkspace(
             layout, rank=rank, world_size=world_size, group=group, device=self.device, wait_limit_ms=wait_limit_ms
         )
@@ -81,7 +129,7 @@ class MoEAllToAll:
         n_max = max(cfg.max_num_tokens * cfg.experts_per_token, 1)
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         i32 = dict(dtype=torch.int32, device=self.device)
-        self._blk_hist = torch.zeros(sms * cfg.num_experts, **i32)
+        self._blk_hist = torch.zeros(2 * sms * cfg.num_experts, **i32)
         self._local_rank = torch.zeros(n_max, **i32)
         self._route = torch.full((n_max, 2), -1, **i32)
         self.expert_num_tokens = torch.zeros(self.num_local_experts, **i32)
@@ -90,6 +138,38 @@ class MoEAllToAll:
         self._off_expert_x = self.ws.offset("expert_x")
         self._off_expert_meta = self.ws.offset("expert_meta")
         self._off_expert_y = self.ws.offset("expert_y")
+        self.engine = None
+        if self.mode == "dedup":
+            names = ("counts", "expert_x", "expert_meta", "expert_y", "land", "tok_rows", "tok_w", "tok_mark", "ret")
+            self.engine = ext.MoeDedupEngine(
+                self.ws.heap, cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens, self.max_recv,
+                cfg.in_dtype, self.partial_fp32, [self.ws.offset(nm) for nm in names], self.expert_y, self._blk_hist,
+                self._route, self.expert_num_tokens, self.ws.wait_limit_ns,
+            )
+        self.trace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+
+    def _guard(self) -> None:
+        """Host-side checks before a launch that waits on peers: an earlier device failure, and
+        (with a monitor) peers that announced their departure or stopped their heartbeat."""
+        self.ws.check()
+        if self.monitor is not None:
+            self.monitor.beat()
+            self.monitor.assert_all_alive()
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Record ``globaltimer`` phase stamps (ns) of the next dedup calls: ``trace[0]`` dispatch =
+        start, counted, rows issued, counts arrived, metadata stored, all sources delivered,
+        replicated, last CTA exit; ``trace[1]`` combine = start, weights exchanged, partials
+        pushed, all partials arrived, -, -, -, last CTA exit."""
+        if self.engine is None:
+            raise RuntimeError("phase stamps exist in the dedup kernels only")
+        if on:
+            self.trace = (torch.zeros(8, dtype=torch.int64, device=self.device),
+                          torch.zeros(8, dtype=torch.int64, device=self.device))
+            self.engine.set_trace(self.trace[0], self.trace[1])
+        else:
+            self.trace = None
+            self.engine.set_trace(None, None)
 
     # -- dispatch ----------------------------------------------------------------------
     def dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -100,10 +180,13 @@ class MoEAllToAll:
             raise ValueError("dp_x / indices do not match the configuration")
         if dp_x.dtype != cfg.in_dtype:
             raise ValueError(f"dp_x is {dp_x.dtype}, configuration says {cfg.in_dtype}")
-        self.ws.check()
+        self._guard()
         x = dp_x.contiguous()
         idx = indices.to(torch.int32).contiguous()
         self._num_tokens = x.shape[0]
+        if self.engine is not None:
+            self.engine.dispatch(x, idx)
+            return self.expert_num_tokens, self.expert_x, self.expert_meta
         self.ext.moe_dispatch(
             self.ws.heap,
             x,
@@ -152,6 +235,21 @@ class MoEAllToAll:
         n = self._num_tokens if num_tokens is None else int(num_tokens)
         if n != self._num_tokens:
             raise ValueError("num_tokens differs from the preceding dispatch")
+        self._guard()
+        if self.engine is not None:
+            # the owner reduces its own expert outputs, so any local tensor of the dispatch layout will do
+            if expert_y.shape != self.expert_y.shape or expert_y.dtype != self.expert_y.dtype:
+                raise ValueError("expert_y does not have the dispatch layout / out_dtype")
+            target = out_tokens
+            if accumulate or not out_tokens.is_contiguous() or out_tokens.dtype != self.cfg.out_dtype:
+                target = torch.empty((max(n, 1), self.cfg.hidden_dim), dtype=self.cfg.out_dtype, device=out_tokens.device)
+            self.engine.combine(target, weights.to(torch.float32).contiguous(), expert_y.contiguous())
+            if target is not out_tokens:
+                if accumulate:
+                    out_tokens[:n] += target[:n].to(out_tokens.dtype)
+                else:
+                    out_tokens[:n] = target[:n].to(out_tokens.dtype)
+            return out_tokens
         if expert_y.data_ptr() != self.expert_y.data_ptr():
             if expert_y.shape != self.expert_y.shape or expert_y.dtype != self.expert_y.dtype:
                 raise ValueError("expert_y does not have the dispatch layout / out_dtype")
@@ -186,12 +284,15 @@ class MoEAllToAll:
             raise ValueError("dp_x does not match the configuration")
         if indices.shape[1] != cfg.experts_per_token:
             raise ValueError("indices do not match the configuration")
-        self.ws.check()
+        self._guard()
         x = dp_x if dp_x.is_contiguous() else dp_x.contiguous()
         idx = indices if (indices.dtype == torch.int32 and indices.is_contiguous()) else indices.to(torch.int32).contiguous()
         w = weights if (weights.dtype == torch.float32 and weights.is_contiguous()) else weights.to(torch.float32).contiguous()
         self._num_tokens = x.shape[0]
         out = torch.empty((x.shape[0], cfg.hidden_dim), dtype=cfg.out_dtype, device=x.device)
+        if self.engine is not None:
+            self.engine.forward(x, idx, w, out, float(scale))
+            return out
         self.ext.moe_forward(
             self.ws.heap, x, idx, w, out, cfg.num_experts, self.max_recv,
             self._off_counts, self._off_expert_x, self._off_expert_meta, self._off_expert_y,
@@ -202,8 +303,10 @@ class MoEAllToAll:
 
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
+        self.ws.check_canaries()
 
     def close(self, collective: bool = False) -> None:
+        self.engine = None
         self.ws.close(collective)
 
 
@@ -214,7 +317,7 @@ class MoEAllToAll:
 _LAYERS: Dict[tuple, MoEAllToAll] = {}
 
 
-def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None) -> MoEAllToAll:
+def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None, mode: Optional[str] = None) -> MoEAllToAll:
     """Workspace creation is collective and costs milliseconds, so layers are cached per
     configuration; the reference rebuilds its helper object on every call
     (all2all/hipv8.py:379) because it owns no persistent state."""
@@ -229,10 +332,11 @@ def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None) -> MoEAllT
         world_size,
         id(group),
         torch.cuda.current_device(),
+        mode or default_mode(),
     )
     layer = _LAYERS.get(key)
     if layer is None:
-        layer = MoEAllToAll(cfg, rank, world_size, group)
+        layer = MoEAllToAll(cfg, rank, world_size, group, mode=mode)
         _LAYERS[key] = layer
     return layer
 
@@ -250,13 +354,14 @@ def _cpu_ranks_share_a_node() -> bool:
     return single_node()
 
 
-def custom_kernel(data: MoEInput, backend: str = "auto") -> torch.Tensor:
+def custom_kernel(data: MoEInput, backend: str = "auto", mode: Optional[str] = None) -> torch.Tensor:
     """Dispatch -> ``* (1 + rank)`` -> combine; returns ``y[num_tokens, hidden]`` in
     ``cfg.out_dtype`` on the rank's device (all2all/reference.py:256-272).
 
     ``backend``: "auto" = the fused kernels for CUDA tensors, the shared-memory operators
     (models/host_ops.py) for CPU tensors when all ranks share a machine, library collectives
-    otherwise; "shm" and "torch" force the latter two."""
+    otherwise; "shm" and "torch" force the latter two.  ``mode`` picks the GPU protocol
+    ("dedup" or "direct", default ``B200_MOE_MODE`` or "dedup")."""
     cfg, rank_data, rank, world_size = data
     x = rank_data.x
     if backend == "shm" or (backend == "auto" and not x.is_cuda and _cpu_ranks_share_a_node()):
@@ -270,5 +375,5 @@ def custom_kernel(data: MoEInput, backend: str = "auto") -> torch.Tensor:
         y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=x.device)
         ata.combine(y, rank_data.weights, em, ey, n_tok)
         return y[: rank_data.num_tokens]
-    layer = get_layer(cfg, rank, world_size)
+    layer = get_layer(cfg, rank, world_size, mode=mode)
     return layer.forward(x, rank_data.indices, rank_data.weights, 1 + rank)

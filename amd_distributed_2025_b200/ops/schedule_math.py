@@ -7,6 +7,11 @@ computes with warps and flags, so that CPU tests can pin the arithmetic:
   (csrc/moe_kernels.cu): rows of lower source ranks first (the exchanged count matrix), then
   this rank's earlier entries with the same expert.  This is the reference's row order
   (all2all/reference.py:79-86, 107-112, 140-146).
+* ``dedup_dispatch`` / ``dedup_combine`` -- the de-duplicating protocol of csrc/moe_dedup.cu with
+  the large kernel's partition of the tokens over CTAs and warps: per-warp histograms, prefix
+  over warps and CTAs, one landed row per (token, destination rank), per-(source, token) row
+  lists on the owner, replication into the expert buffers, and the owner-side weighted
+  pre-reduction with one returned row per (source, token).
 * ``gemm_tile_order`` -- the order in which a CTA (pair) scheduler of ``gemm_rs_kernel`` visits
   its work items: K slices innermost, column tiles inside a band of row groups, bands along
   the row-group sequence that is rotated so the rank's own rows come last
@@ -91,3 +96,78 @@ def expected_arrivals(world_size: int, splits: int, fused_own: bool) -> int:
     """Arrivals per (tile, 32-row quarter) counter: every (virtual) rank once, minus this rank when
     it keeps its own partial in registers."""
     return world_size - 1 if (fused_own and splits == 1) else world_size * splits
+
+
+def dedup_dispatch(indices_per_rank: Sequence[Sequence[Sequence[int]]], num_experts: int, max_recv: int,
+                   grid: int = 3, warps: int = 8):
+    """The dedup dispatch as the large kernel partitions it: CTA ``b`` of ``grid`` owns tokens
+    ``[b * tpc, (b + 1) * tpc)``, its warp ``w`` a contiguous part of them.  Returns per owner rank
+    ``(meta, tok_rows, landed)``: ``meta[row] = (expert, src, token, k)``, ``tok_rows[(src, t)]`` the
+    k-list of final rows on that owner (or -1), ``landed`` the set of ``(src, t)`` that crossed to it."""
+    ws = len(indices_per_rank)
+    e_local = num_experts // ws
+    counts = [[0] * num_experts for _ in range(ws)]
+    per_rank = []
+    for r, idx in enumerate(indices_per_rank):
+        n_tok = len(idx)
+        tpc = -(-n_tok // grid) if n_tok else 0
+        tpw = -(-tpc // warps) if tpc else 0
+        whist = [[[0] * num_experts for _ in range(warps)] for _ in range(grid)]
+        ranges = {}
+        for b in range(grid):
+            c0, c1 = min(n_tok, b * tpc), min(n_tok, b * tpc + tpc)
+            for w in range(warps):
+                t0 = min(c1, c0 + w * tpw)
+                t1 = min(c1, t0 + tpw)
+                ranges[(b, w)] = (t0, t1)
+                for t in range(t0, t1):
+                    for e in idx[t]:
+                        whist[b][w][e] += 1
+        blk = [[sum(whist[b][w][e] for w in range(warps)) for e in range(num_experts)] for b in range(grid)]
+        for e in range(num_experts):
+            counts[r][e] = sum(blk[b][e] for b in range(grid))
+        per_rank.append((whist, blk, ranges))
+    owners = [({}, {}, set()) for _ in range(ws)]
+    for r, idx in enumerate(indices_per_rank):
+        whist, blk, ranges = per_rank[r]
+        for b in range(grid):
+            base = [sum(blk[g][e] for g in range(b)) + sum(counts[s][e] for s in range(r)) for e in range(num_experts)]
+            for w in range(warps):
+                run = [sum(whist[b][v][e] for v in range(w)) for e in range(num_experts)]  # exclusive prefix over warps
+                t0, t1 = ranges[(b, w)]
+                for t in range(t0, t1):
+                    rows = []
+                    for kk, e in enumerate(idx[t]):
+                        slot = base[e] + run[e]
+                        run[e] += 1
+                        dst = e // e_local
+                        row = (e % e_local) * max_recv + slot if slot < max_recv else -1
+                        rows.append((dst, row))
+                        if row >= 0:
+                            owners[dst][0][row] = (e, r, t, kk)
+                    for d in {dst for dst, _ in rows}:
+                        owners[d][1][(r, t)] = [row if dst == d else -1 for dst, row in rows]
+                        if d != r:
+                            owners[d][2].add((r, t))
+    return counts, owners
+
+
+def dedup_combine(owners, weights_per_rank, expert_y_per_rank, num_tokens: Sequence[int], hidden: int):
+    """Owner-side pre-reduction and source-side sum: ``out[src][t] = sum over owners d (ascending) of
+    sum over the entries of (src, t) on d (ascending k) of w * expert_y[d][row]``; plain floats."""
+    ws = len(owners)
+    out = [[[0.0] * hidden for _ in range(num_tokens[r])] for r in range(ws)]
+    for d in range(ws):
+        _, tok_rows, _ = owners[d]
+        for (src, t), rows in sorted(tok_rows.items()):
+            part = [0.0] * hidden
+            for kk, row in enumerate(rows):
+                if row < 0:
+                    continue
+                w = weights_per_rank[src][t][kk]
+                y = expert_y_per_rank[d][row]
+                for h in range(hidden):
+                    part[h] += w * y[h]
+            for h in range(hidden):
+                out[src][t][h] += part[h]
+    return out

@@ -23,6 +23,19 @@ import torch.distributed as dist
 from ..utils.status import StatusError, describe_status
 
 DEFAULT_WAIT_LIMIT_MS = float(os.environ.get("B200_WAIT_LIMIT_MS", "10000"))
+CANARY_BYTE = 0xA5
+
+
+def checked() -> bool:
+    """``B200_CHECKED=1`` selects the checked flavour: guard words between the regions of
+    every slab (verified by ``check()``), and range checks before every remote store of the
+    GEMM epilogue.  It stands in for a memory sanitizer, which the reference does not use
+    either (its guards are the hand-written range checks of all2all/hipv8.py:118,124,198,205)."""
+    return os.environ.get("B200_CHECKED", "0").strip() not in ("", "0", "false", "False")
+
+
+def checked_guard_bytes() -> int:
+    return 1024 if checked() else 0
 
 
 def _align_up(x: int, a: int) -> int:
@@ -32,10 +45,12 @@ def _align_up(x: int, a: int) -> int:
 class SlabLayout:
     """Deterministic bump allocator over one slab; offsets are bytes from the slab base."""
 
-    def __init__(self, header_bytes: int, align: int = 1024):
+    def __init__(self, header_bytes: int, align: int = 1024, guard_bytes: int = 0):
         self.align = align
         self.cursor = _align_up(header_bytes, align)
         self.regions: Dict[str, Tuple[int, int]] = {}
+        self.guard_bytes = int(guard_bytes)
+        self.guards: List[Tuple[int, int]] = []  # (offset, bytes) of the canary areas after each region
 
     def add(self, name: str, nbytes: int, align: Optional[int] = None) -> int:
         if name in self.regions:
@@ -44,6 +59,11 @@ class SlabLayout:
         off = _align_up(self.cursor, a)
         self.regions[name] = (off, int(nbytes))
         self.cursor = off + int(nbytes)
+        if self.guard_bytes:
+            # a canary area right behind the region: an overrun of the region lands here first
+            g = _align_up(self.cursor, 16)
+            self.guards.append((g, self.guard_bytes))
+            self.cursor = g + self.guard_bytes
         return off
 
     def offset(self, name: str) -> int:
@@ -89,9 +109,25 @@ class SymmetricWorkspace:
         group=None,
         device: Optional[torch.device] = None,
         wait_limit_ms: Optional[float] = None,
+        poison_on_timeout: bool = False,
+        heap=None,
     ):
         from ..ops import _ext
 
+        # A protocol whose flags do not carry the call number (the arrival counters of the fused
+        # GEMM) cannot be trusted after an expired wait: late arrivals of the failed call would
+        # satisfy the next one.  Such a workspace stays poisoned until recover() is run collectively.
+        self.poison_on_timeout = bool(poison_on_timeout)
+        self.poisoned: Optional[dict] = None
+        self._canary_views: List[torch.Tensor] = []
+        if heap is not None:
+            # pre-built heap (tests drive the host-side state machine with a stand-in)
+            self.ext, self.group, self.heap = None, group, heap
+            self.world_size, self.rank = world_size or 1, rank or 0
+            self.device, self.layout, self.epochs = device, layout, EpochCounter()
+            self.wait_limit_ns = int((wait_limit_ms if wait_limit_ms is not None else DEFAULT_WAIT_LIMIT_MS) * 1e6)
+            self._closed = False
+            return
         self.ext = _ext.load()
         self.group = group
         initialized = dist.is_available() and dist.is_initialized()
@@ -115,6 +151,10 @@ class SymmetricWorkspace:
             self.heap.open_peers(handles)
             dist.barrier(group=group)
         self._closed = False
+        for off, nbytes in layout.guards:
+            view = self.heap.view(off, [nbytes], torch.uint8)
+            view.fill_(CANARY_BYTE)
+            self._canary_views.append(view)
 
     # -- memory ------------------------------------------------------------------------
     def view(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
@@ -142,15 +182,54 @@ class SymmetricWorkspace:
         return self.heap.status_sync() if sync else self.heap.status()
 
     def check(self, sync: bool = False) -> None:
-        """Raise ``StatusError`` if a kernel recorded a failure (expired wait, bad index)."""
+        """Raise ``StatusError`` if a kernel recorded a failure (expired wait, bad index), or if
+        an earlier expired wait poisoned the workspace (see ``recover``)."""
+        if self.poisoned is not None:
+            raise StatusError(
+                describe_status(self.poisoned, self.rank) + "; the workspace stays unusable until recover() "
+                "has been called by all ranks together", self.poisoned)
         if not sync and self.heap.status_code() == 0:
             return
         st = self.status(sync)
         if st["code"] != 0:
+            if self.poison_on_timeout and st["code"] == 1 and self.world_size > 1:
+                self.poisoned = dict(st)
             raise StatusError(describe_status(st, self.rank), st)
 
     def reset_status(self) -> None:
+        """Clear the status record.  Does not lift a poisoning: that takes ``recover``."""
         self.heap.reset_status()
+
+    def recover(self, zero_regions: Sequence[str] = ()) -> None:
+        """Collective recovery after an expired wait: every rank drains its stream, the ranks
+        meet on the host, each zeroes the named regions of its own slab (arrival counters) and
+        its status record, the call numbers restart, and the ranks meet again before anybody
+        launches.  All surviving ranks of the group must call it."""
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        initialized = dist.is_available() and dist.is_initialized()
+        if self.world_size > 1 and initialized:
+            dist.barrier(group=self.group)
+        for name in zero_regions:
+            off, size = self.layout.regions[name]
+            self.heap.view(off, [size], torch.uint8).zero_()
+        self.heap.reset_status()
+        self.epochs = EpochCounter()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        if self.world_size > 1 and initialized:
+            dist.barrier(group=self.group)
+        self.poisoned = None
+
+    def check_canaries(self) -> None:
+        """With guard areas (``B200_CHECKED=1``): raise if any byte behind a region changed."""
+        for (off, nbytes), view in zip(self.layout.guards, self._canary_views):
+            if not bool((view == CANARY_BYTE).all()):
+                bad = int((view != CANARY_BYTE).nonzero()[0])
+                name = next((n for n, (o, sz) in self.layout.regions.items() if o + sz <= off < o + sz + 32), "?")
+                raise StatusError(f"rank {self.rank}: guard area behind region {name!r} was overwritten "
+                                  f"(first bad byte at slab offset {off + bad})", {"code": 2, "phase": 0, "peer": -1,
+                                                                                 "detail": off + bad, "epoch": 0, "seen": 0})
 
     def close(self, collective: bool = False) -> None:
         """Release the slab.  With ``collective=True`` (all ranks call it together, idle) the

@@ -22,8 +22,14 @@ _REASON_BITS = {
 
 
 class ClockSampler:
-    def __init__(self, gpu_index: int, interval_s: float = 0.005):
+    """``gpu_index`` is the CUDA ordinal; NVML and ``nvidia-smi`` number the physical GPUs and
+    ignore ``CUDA_VISIBLE_DEVICES``, so pass the device's ``uuid``
+    (``torch.cuda.get_device_properties(i).uuid``) whenever a device mask may be in force:
+    the handle is then resolved by UUID and the index is only the fallback."""
+
+    def __init__(self, gpu_index: int, interval_s: float = 0.005, uuid: Optional[str] = None):
         self.gpu_index = gpu_index
+        self.uuid = None if not uuid else (uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
         self.interval_s = interval_s
         self._samples: List[tuple] = []  # (sm_mhz, power_w, reasons_mask)
         self._sm_max: Optional[float] = None
@@ -38,7 +44,17 @@ class ClockSampler:
 
             pynvml.nvmlInit()
             self._nvml = pynvml
-            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self._handle = None
+            if self.uuid is not None:
+                try:
+                    self._handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+                except Exception:  # noqa: BLE001 - older bindings want bytes
+                    try:
+                        self._handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode())
+                    except Exception:  # noqa: BLE001
+                        self._handle = None
+            if self._handle is None:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
             self._sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
         except Exception:  # noqa: BLE001 - fall back to one nvidia-smi query at stop()
             self._nvml = None
@@ -100,7 +116,7 @@ class ClockSampler:
                   "clocks_event_reasons.sw_power_cap")
         try:
             out = subprocess.run(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={fields}", "--format=csv,noheader,nounits"],
+                ["nvidia-smi", f"--id={self.uuid or self.gpu_index}", f"--query-gpu={fields}", "--format=csv,noheader,nounits"],
                 capture_output=True, text=True, timeout=10,
             ).stdout.strip().splitlines()[0]
             parts = [p.strip() for p in out.split(",")]

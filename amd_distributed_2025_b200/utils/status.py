@@ -16,6 +16,8 @@ PHASES = {
     6: "gemm_pipeline",
     7: "barrier",
     8: "selftest",
+    9: "moe_weights",
+    10: "moe_return",
 }
 
 

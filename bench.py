@@ -42,13 +42,48 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-from amd_distributed_2025_b200 import contract  # noqa: E402
+from amd_distributed_2025_b200 import contract, oracle  # noqa: E402
 from amd_distributed_2025_b200.harness import reference_arm  # noqa: E402
 from amd_distributed_2025_b200.utils import timing  # noqa: E402
 from amd_distributed_2025_b200.utils.clocks import ClockSampler  # noqa: E402
 
 METRIC = "dispatch+combine us, GEMM-RS us (max over ranks), geomean over headline configs"
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_MEASURED = os.path.join(ROOT, "baseline", "reference_measured.json")
+# how a configuration grows with the number of GPUs: MoE keeps the tokens per rank (weak),
+# GEMM-RS keeps the global problem and splits K (strong)
+SCALING = {"moe": "weak", "gemm_rs": "strong"}
+
+
+def stored_reference_value(n_gpus: int):
+    """Geomean of the reference arm on this benchmark at ``n_gpus`` from an earlier run on the
+    same kind of machine (baseline/reference_measured.json), or None."""
+    try:
+        with open(REF_MEASURED, "r", encoding="utf-8") as fh:
+            return float(json.load(fh)["per_n"][str(n_gpus)]["value_us"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
+def verify_output(item, y: torch.Tensor, rank: int, ws: int, device: torch.device) -> bool:
+    """Compare a configuration's last result with the communication-free oracle (outside every
+    timed region).  MoE: the task's tolerance against the expected combine; GEMM-RS: relative
+    error against the un-rounded fp32 sum over all ranks' operands (the task tolerance is vacuous
+    or noise-dominated for these operand distributions, see oracle.outlier_fraction)."""
+    if item["kind"] == "moe":
+        want = oracle.moe_expected_output(item["cfg"], item["data"], ws, emulate_reference_rounding=True)
+        ok, _ = oracle.check_moe_output(y, want)
+        return bool(ok)
+    c = item["spec"]
+    rows = c["m"] // ws
+    acc = torch.zeros(rows, c["n"], dtype=torch.float32, device=device)
+    for r in range(ws):  # regenerate the peers' operands here instead of moving them between GPUs
+        a, w, _ = contract.make_gemm_rs_inputs(r, ws, c["m"], c["n"], c["k"], c["has_bias"], c["seed"], device=device)
+        acc += a[rank * rows:(rank + 1) * rows].float() @ w.float().T
+        del a, w
+    if item["bias"] is not None:
+        acc += ws * item["bias"].float()
+    return oracle.relative_error(y, acc) < 5e-3
 
 
 # --------------------------------------------------------------------------------------
@@ -86,7 +121,7 @@ def build_inputs(rank: int, ws: int, device: torch.device):
 # --------------------------------------------------------------------------------------
 class Ours:
     name = "ours"
-    kernels_per_call = {"moe": 3, "gemm_rs": 1}  # dispatch + expert scale + combine; fused GEMM-RS
+    kernels_per_call = {"moe": 2, "gemm_rs": 1}  # dispatch (with the expert op) + combine; fused GEMM-RS
 
     def __init__(self, rank: int, ws: int):
         from amd_distributed_2025_b200.models import gemm_rs, moe_all2all
@@ -240,7 +275,7 @@ def main() -> int:
     _barrier(ws)
 
     # ---- device-timed region: exactly `steps` steps ---------------------------------------
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, uuid=str(torch.cuda.get_device_properties(local_rank).uuid))
     if rank == 0:
         sampler.start()
     torch.cuda.synchronize()
@@ -263,6 +298,19 @@ def main() -> int:
     torch.cuda.synchronize()
     impl.check()
 
+    # ---- outputs against the oracle (untimed; every rank checks its own slice) ----------------
+    checked: Dict[str, bool] = {}
+    for it in items:
+        y = impl.call(it)
+        torch.cuda.synchronize()
+        ok = verify_output(it, y, rank, ws, device)
+        if ws > 1:
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+        checked[it["name"]] = ok
+        del y
+
     per_config = {}
     for it in items:
         name = it["name"]
@@ -273,6 +321,8 @@ def main() -> int:
             "median_us": statistics.median(d) * 1e3,
             "min_us": min(d) * 1e3,
             "e2e_us": statistics.fmean(e) * 1e3,
+            "scaling": SCALING[it["kind"]],
+            "checked": checked[name],
         }
     if rank == 0:
         value = timing.geomean([v["us"] for v in per_config.values()])
@@ -280,6 +330,14 @@ def main() -> int:
         h2d = sum(sum(t.numel() * t.element_size() for t in it["host"].values()) for it in items)
         d2h = sum(t.numel() * t.element_size() for t in out_host.values())
         launches = sum(impl.kernels_per_call[it["kind"]] for it in items) * args.steps
+        aggregates = {}
+        for kind, label in SCALING.items():
+            names = [it["name"] for it in items if it["kind"] == kind]
+            if names:
+                aggregates[kind] = {"value": timing.geomean([per_config[nm]["us"] for nm in names]),
+                                    "e2e": timing.geomean([per_config[nm]["e2e_us"] for nm in names]),
+                                    "unit": "us", "scaling": label, "configs": names}
+        ref_value = stored_reference_value(ws) if args.only is None else None
         line = {
             "metric": METRIC,
             "value": value,
@@ -290,8 +348,12 @@ def main() -> int:
             "warmup": warmup,
             "ms_per_step": sum(v["us"] for v in per_config.values()) / 1e3,
             "higher_is_better": False,
-            "scaling": "strong",
-            "vs_baseline": None,
+            # the geomean mixes weak-scaled MoE and strong-scaled GEMM-RS configurations: read the
+            # curve per configuration (per_config_us[*].scaling) or per family (aggregates)
+            "scaling": "mixed",
+            "vs_baseline": (value / ref_value) if ref_value else None,
+            "baseline_source": "baseline/reference_measured.json (reference arm on B200, same N)" if ref_value else None,
+            "checked": all(checked.values()),
             "dtype": "bf16",
             "data": "synthetic (seeded); random-init operands of the named shapes",
             "config": {
@@ -304,6 +366,7 @@ def main() -> int:
                 "timing": "CUDA events per call, max over ranks, mean over steps, geomean over configs",
             },
             "per_config_us": per_config,
+            "aggregates": aggregates,
             "e2e": {"value": e2e_value, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "clocks": clocks,

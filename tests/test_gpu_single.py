@@ -45,6 +45,7 @@ def test_bounded_wait_times_out_and_context_survives():
     ws.close()
 
 
+@pytest.mark.parametrize("mode", ["dedup", "direct"])
 @pytest.mark.parametrize(
     "E,k,H,T,dtype,fixed",
     [
@@ -53,37 +54,62 @@ def test_bounded_wait_times_out_and_context_survives():
         (128, 4, 2880, 32, torch.float16, None),
         (256, 8, 7168, 128, torch.bfloat16, 128),
         (16, 2, 256, 32, torch.float32, 32),
-        (64, 6, 1024, 1024, torch.bfloat16, 1024),
+        (64, 6, 1024, 1024, torch.bfloat16, 1024),  # > 4096 entries: the grid-barrier kernels
+        (256, 8, 512, 600, torch.float16, 600),
         (8, 2, 250, 5, torch.float16, 5),  # row size not a multiple of 16 bytes: scalar paths
     ],
 )
-def test_moe_world1_matches_oracle(E, k, H, T, dtype, fixed):
+def test_moe_world1_matches_oracle(E, k, H, T, dtype, fixed, mode):
     from amd_distributed_2025_b200.models import moe_all2all
 
-    cfg, data, rank, ws = contract.make_moe_inputs(E, k, H, T, 7, 0, 1, device="cuda", dtype=dtype,
-                                                   fixed_num_tokens=fixed, routing="zipf" if T >= 1024 else "uniform",
-                                                   weights="softmax")
-    layer = moe_all2all.get_layer(cfg, 0, 1)
-    got = layer.dispatch(data.x, data.indices)
-    torch.cuda.synchronize()
-    layer.check()
-    ok, msg = oracle.compare_dispatch_layout(got, oracle.moe_dispatch_oracle(cfg, [data], 0))
-    assert ok, msg
-    for _ in range(3):  # repeated calls exercise the epoch-numbered flags
-        y = moe_all2all.custom_kernel((cfg, data, 0, 1))
-    torch.cuda.synchronize()
-    layer.check()
-    want = oracle.moe_expected_output(cfg, data, 1)
-    ok, msg = oracle.check_moe_output(y, want)
-    assert ok, msg
-    assert oracle.relative_error(y, oracle.moe_expected_output(cfg, data, 1, acc_dtype=torch.float64)) < 5e-3
+    for it in range(3):  # new inputs (and token counts) every call: nothing of the previous call may survive
+        n_tok = None if fixed is None else max(fixed - 3 * it, 1)
+        cfg, data, rank, ws = contract.make_moe_inputs(E, k, H, T, 7 + it, 0, 1, device="cuda", dtype=dtype,
+                                                       fixed_num_tokens=n_tok, routing="zipf" if T >= 600 else "uniform",
+                                                       weights="softmax")
+        layer = moe_all2all.get_layer(cfg, 0, 1, mode=mode)
+        if it == 1:
+            got = layer.dispatch(data.x, data.indices)
+            torch.cuda.synchronize()
+            layer.check()
+            ok, msg = oracle.compare_dispatch_layout(got, oracle.moe_dispatch_oracle(cfg, [data], 0))
+            assert ok, msg
+            layer.expert_scale(1.0)
+            y = torch.empty(data.num_tokens, H, dtype=dtype, device="cuda")
+            layer.combine(y, data.weights, got[2], layer.expert_y, got[0], data.num_tokens)
+        else:
+            y = moe_all2all.custom_kernel((cfg, data, 0, 1), mode=mode)
+        torch.cuda.synchronize()
+        layer.check()
+        ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, data, 1))
+        assert ok, (it, msg)
+        assert oracle.relative_error(y, oracle.moe_expected_output(cfg, data, 1, acc_dtype=torch.float64)) < 5e-3
 
 
-def test_moe_combine_accepts_foreign_expert_y():
+def test_moe_dedup_fp32_partial_rows_and_phase_stamps():
+    from amd_distributed_2025_b200.models import moe_all2all
+
+    cfg, data, _, _ = contract.make_moe_inputs(32, 4, 1024, 96, 11, 0, 1, device="cuda", dtype=torch.bfloat16,
+                                               fixed_num_tokens=96, weights="softmax")
+    layer = moe_all2all.MoEAllToAll(cfg, 0, 1, mode="dedup", partial_dtype=torch.float32)
+    layer.enable_trace()
+    y = layer.forward(data.x, data.indices, data.weights, 1.0)
+    torch.cuda.synchronize()
+    layer.check()
+    ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, data, 1))
+    assert ok, msg
+    d, c = layer.trace[0].tolist(), layer.trace[1].tolist()
+    assert all(v > 0 for v in d) and d[:7] == sorted(d[:7]) and d[7] >= d[6]  # dispatch phases in order
+    assert c[0] > 0 and c[7] >= c[2] >= c[1] >= c[0] and c[0] >= d[0]
+    layer.close()
+
+
+@pytest.mark.parametrize("mode", ["dedup", "direct"])
+def test_moe_combine_accepts_foreign_expert_y(mode):
     from amd_distributed_2025_b200.models import moe_all2all
 
     cfg, data, _, _ = contract.make_moe_inputs(32, 4, 512, 64, 3, 0, 1, device="cuda", fixed_num_tokens=64)
-    layer = moe_all2all.get_layer(cfg, 0, 1)
+    layer = moe_all2all.get_layer(cfg, 0, 1, mode=mode)
     n_tok, ex, em = layer.dispatch(data.x, data.indices)
     ey = ex.clone() * 3  # an ordinary tensor, not the symmetric buffer
     y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device="cuda")
@@ -93,19 +119,24 @@ def test_moe_combine_accepts_foreign_expert_y():
     assert torch.allclose(y[: data.num_tokens].float(), want.float(), rtol=1e-2, atol=5e-3)
 
 
-def test_moe_bad_expert_id_is_reported_not_faulted():
+@pytest.mark.parametrize("mode", ["dedup", "direct"])
+def test_moe_bad_expert_id_is_reported_not_faulted(mode):
     from amd_distributed_2025_b200.models import moe_all2all
     from amd_distributed_2025_b200.utils.status import StatusError
 
     cfg, data, _, _ = contract.make_moe_inputs(16, 2, 128, 8, 3, 0, 1, device="cuda", fixed_num_tokens=8)
-    layer = moe_all2all.MoEAllToAll(cfg, 0, 1)
+    layer = moe_all2all.MoEAllToAll(cfg, 0, 1, mode=mode)
     bad = data.indices.clone()
     bad[2, 1] = 99
-    layer.dispatch(data.x, bad)
+    y = layer.forward(data.x, bad, data.weights, 2.0)
     torch.cuda.synchronize()
     with pytest.raises(StatusError) as err:
         layer.check()
     assert err.value.code == "bad_index"
+    # the other entries were served: every token but the one with the bad id has its full result
+    want = (data.x.float() * 2 * data.weights.sum(1, keepdim=True)).to(cfg.out_dtype)
+    keep = [t for t in range(8) if t != 2]
+    assert torch.allclose(y[keep].float(), want[keep].float(), rtol=1e-2, atol=5e-3)
     layer.ws.reset_status()
     layer.close()
 

@@ -197,3 +197,99 @@ def test_clock_sampler_only_reads_and_summarises_the_samples_under_load(monkeypa
     assert out["power_w_max"] == 1000.0
     assert out["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
     assert out["samples_under_load"] < out["samples"]
+
+
+def test_clock_sampler_resolves_the_device_by_uuid_under_a_device_mask(monkeypatch):
+    """CUDA ordinal 0 of a masked process is physical GPU 5: the sampler must read GPU 5's
+    clocks (handle by UUID), not those of physical GPU 0, which may be another user's."""
+    import sys
+    import types
+
+    from amd_distributed_2025_b200.utils.clocks import ClockSampler
+
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: None
+    fake.nvmlShutdown = lambda: None
+    physical = {f"GPU-0000-{i}": ("handle", i) for i in range(8)}
+    fake.nvmlDeviceGetHandleByUUID = lambda u: physical[u if isinstance(u, str) else u.decode()]
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("handle", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965
+    fake.nvmlDeviceGetClockInfo = lambda h, kind: 1000 + h[1]  # a clock that tells which GPU was read
+    fake.nvmlDeviceGetPowerUsage = lambda h: 500_000
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+
+    s = ClockSampler(0, interval_s=0.001, uuid="0000-5")  # torch prints the UUID without the "GPU-" prefix
+    s.start()
+    out = s.stop()
+    assert out["sm_mhz"] == 1005
+    s = ClockSampler(3, interval_s=0.001)  # no UUID given: the index is all there is
+    s.start()
+    assert s.stop()["sm_mhz"] == 1003
+
+
+def test_workspace_stays_poisoned_after_a_timeout_until_collective_recovery():
+    """Arrival counters that are plain counts cannot be trusted after an expired wait (late
+    arrivals of the failed call would satisfy the next one): a workspace created with
+    ``poison_on_timeout`` keeps raising after ``reset_status`` until ``recover`` has zeroed the
+    counters.  Driven here with a stand-in heap, no GPU."""
+    from amd_distributed_2025_b200.parallel.symm_mem import SlabLayout, SymmetricWorkspace
+    from amd_distributed_2025_b200.utils.status import StatusError
+
+    class FakeHeap:
+        def __init__(self):
+            self.word = {"code": 0, "phase": 0, "peer": -1, "detail": 0, "epoch": 0, "seen": 0}
+            self.mem = torch.full((8192,), 7, dtype=torch.uint8)
+
+        def status_code(self):
+            return self.word["code"]
+
+        def status(self):
+            return dict(self.word)
+
+        status_sync = status
+
+        def reset_status(self):
+            self.word = dict(self.word, code=0)
+
+        def view(self, off, shape, dtype):
+            return self.mem[off:off + shape[0]]
+
+    lay = SlabLayout(4096)
+    lay.add("counters0", 256)
+    lay.add("counters1", 256)
+    for poison in (True, False):
+        heap = FakeHeap()
+        ws = SymmetricWorkspace(lay, rank=0, world_size=2, heap=heap, poison_on_timeout=poison)
+        ws.check()
+        ws.next_epoch("gemm_rs")
+        heap.word.update(code=1, phase=5, peer=1)  # a peer's partial rows never arrived
+        with pytest.raises(StatusError):
+            ws.check()
+        ws.reset_status()
+        if not poison:
+            ws.check()  # flags that carry the call number need no more than that
+            continue
+        with pytest.raises(StatusError) as err:
+            ws.check()
+        assert "recover" in str(err.value)
+        ws.recover(("counters0", "counters1"))
+        ws.check()
+        assert int(heap.mem[4096:4096 + 256].sum()) == 0 and int(heap.mem[5120:5120 + 256].sum()) == 0
+        assert ws.epochs.current("gemm_rs") == 0  # call numbers (and with them the staging parity) restart
+
+
+def test_checked_layout_puts_a_guard_area_behind_every_region():
+    from amd_distributed_2025_b200.parallel.symm_mem import SlabLayout
+
+    plain, guarded = SlabLayout(4096), SlabLayout(4096, guard_bytes=1024)
+    for lay in (plain, guarded):
+        lay.add("a", 1000)
+        lay.add("b", 5000)
+    assert not plain.guards and len(guarded.guards) == 2
+    (g0, n0), (g1, n1) = guarded.guards
+    a_off, a_len = guarded.regions["a"]
+    b_off, b_len = guarded.regions["b"]
+    assert a_off + a_len <= g0 < g0 + n0 <= b_off and b_off + b_len <= g1 and g1 + n1 <= guarded.total_bytes
+    assert not guarded.overlaps()

@@ -68,3 +68,37 @@ def test_ownership_and_arrival_counts():
     assert sm.expected_arrivals(8, 1, fused_own=True) == 7
     assert sm.expected_arrivals(8, 1, fused_own=False) == 8
     assert sm.expected_arrivals(2, 3, fused_own=True) == 6  # K slices are always staged
+
+
+@pytest.mark.parametrize("ws,E,k,T,grid", [(1, 8, 2, 9, 3), (2, 16, 2, 37, 4), (4, 64, 6, 21, 2), (8, 64, 6, 40, 5)])
+def test_dedup_protocol_reproduces_oracle_layout_and_output(ws, E, k, T, grid):
+    """One landed row per (token, destination rank), replicated by the owner, gives the oracle's
+    dispatch layout; owner-side pre-reduced rows summed by the source give the oracle's output."""
+    H = 4
+    cfg = MoEConfig(E, k, H, T, torch.float32, torch.float32)
+    data = []
+    for r in range(ws):
+        g = torch.Generator().manual_seed(7 + r)
+        data.append(RankTestData(cfg, g, r, device="cpu", fixed_num_tokens=T if r % 2 == 0 else max(T - 5, 0)))
+    max_recv = cfg.max_recv(ws)
+    counts, owners = sm.dedup_dispatch([d.indices.tolist() for d in data], E, max_recv, grid=grid)
+    e_local = E // ws
+    expert_y = []
+    for owner in range(ws):
+        n_tok, ex, meta = oracle.moe_dispatch_oracle(cfg, data, owner)
+        got_meta, tok_rows, landed = owners[owner]
+        rows = {el * max_recv + s: tuple(meta[el, s, :4].tolist()) for el in range(e_local) for s in range(int(n_tok[el]))}
+        assert got_meta == rows
+        # replication: every final row is fed by the landed (or local) row of its (src, token)
+        for (src, t), lst in tok_rows.items():
+            assert (src, t) in landed or src == owner
+            for kk, row in enumerate(lst):
+                if row >= 0:
+                    assert torch.equal(ex.reshape(-1, H)[row], data[src].x[t]) and rows[row][1:] == (src, t, kk)
+        # a token lands at most once per destination: that is the whole point
+        assert len(landed) == len({(s, t) for (s, t) in tok_rows if s != owner})
+        expert_y.append((ex.reshape(-1, H) * (1 + owner)).tolist())
+    out = sm.dedup_combine(owners, [d.weights.tolist() for d in data], expert_y, [d.num_tokens for d in data], H)
+    for r in range(ws):
+        want = oracle.moe_expected_output(cfg, data[r], ws)
+        assert torch.allclose(torch.tensor(out[r], dtype=torch.float32).reshape(-1, H), want, rtol=1e-5, atol=1e-5)

@@ -41,6 +41,8 @@ def _run_both(lib, layer, cfg, data, out):
 
     ex, em, en, route = out
     idx = data.indices.to(torch.int32).contiguous()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = lib.b200_moe_dispatch_noalloc(
         data.x.data_ptr(), idx.data_ptr(), data.num_tokens, cfg.experts_per_token,
         cfg.hidden_dim * data.x.element_size(), cfg.num_experts, cfg.max_num_tokens,
@@ -49,7 +51,8 @@ def _run_both(lib, layer, cfg, data, out):
     )
     assert rc == 0, lib.b200_moe_dispatch_noalloc_error().decode()
     assert lib.b200_moe_dispatch_noalloc_status() == 0
-    return ref, (en, ex, em, route[: data.num_tokens * cfg.experts_per_token])
+    moved = free_before - torch.cuda.mem_get_info()[0]  # device memory taken while the C call ran
+    return ref, (en, ex, em, route[: data.num_tokens * cfg.experts_per_token]), moved
 
 
 def _assert_same(cfg, ref, got):
@@ -78,11 +81,48 @@ def test_noalloc_dispatch_matches_regular_entry_point_twice():
         torch.zeros(T * k, 2, dtype=torch.int32, device="cuda"),
     )
     try:
-        for data in (first, second):  # two calls in a row on the shared scratch array
-            ref, got = _run_both(lib, layer, cfg, data, out)
+        for i, data in enumerate((first, second)):  # two calls in a row on the shared scratch array
+            ref, got, moved = _run_both(lib, layer, cfg, data, out)
             _assert_same(cfg, ref, got)
+            # the property the entry point exists for: the device's free memory does not move
+            # across a call (the very first one may pay for the lazy loading of the kernel image)
+            assert i == 0 or moved == 0
     finally:
         layer.close()
+
+
+def test_noalloc_dispatch_empty_batch_and_bad_expert_id():
+    lib = _lib()
+    E, k, H, T = 16, 2, 256, 8
+    cfg, data, _, _ = contract.make_moe_inputs(E, k, H, T, 5, 0, 1, device="cuda", fixed_num_tokens=T)
+    ex = torch.zeros(E, T, H, dtype=cfg.in_dtype, device="cuda")
+    em = torch.zeros(E, T, 5, dtype=torch.int32, device="cuda")
+    en = torch.full((E,), -1, dtype=torch.int32, device="cuda")
+    route = torch.zeros(T * k, 2, dtype=torch.int32, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(idx, n_tok):
+        return lib.b200_moe_dispatch_noalloc(data.x.data_ptr(), idx.data_ptr(), n_tok, k, H * data.x.element_size(), E, T,
+                                             ex.data_ptr(), em.data_ptr(), en.data_ptr(), route.data_ptr(), stream)
+
+    idx = data.indices.to(torch.int32).contiguous()
+    assert call(idx, 0) == 0  # no tokens: every expert ends up empty
+    assert lib.b200_moe_dispatch_noalloc_status() == 0
+    assert en.tolist() == [0] * E
+    assert lib.b200_moe_dispatch_noalloc(data.x.data_ptr(), idx.data_ptr(), T, k, H * 2, E, T, None, em.data_ptr(),
+                                         en.data_ptr(), route.data_ptr(), stream) == -5  # a null output buffer
+    bad = idx.clone()
+    bad[3, 1] = E  # one past the last expert
+    assert call(bad, T) == 0
+    assert lib.b200_moe_dispatch_noalloc_status() == 2  # reported, not faulted
+    assert route[3 * k + 1].tolist() == [-1, -1]
+    good = [i for i in range(T * k) if i != 3 * k + 1]
+    rows = route[good, 1].tolist()
+    flat = bad.reshape(-1).tolist()
+    for i, row in zip(good, rows):  # every other entry was delivered to its expert
+        assert row // T == flat[i] and torch.equal(ex.reshape(E * T, H)[row], data.x[i // k])
+    assert int(en.sum()) == T * k - 1
+    assert call(idx, T) == 0 and lib.b200_moe_dispatch_noalloc_status() == 0  # the next call starts clean
 
 
 def test_noalloc_dispatch_rejects_sizes_beyond_its_scratch():
