@@ -395,7 +395,8 @@ class MoeDedupEngine {
 void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
              at::Tensor out, double bias_scale, bool bias_at_source, int64_t off_stage, int64_t off_counters, int64_t epoch,
              int64_t timeout_ns, int64_t max_ctas, int64_t block_n, int64_t cta_pair, int64_t splits,
-             const c10::optional<at::Tensor>& trace, int64_t debug, bool fuse_own, bool tma_store, bool force_staged) {
+             const c10::optional<at::Tensor>& trace, int64_t debug, bool fuse_own, bool tma_store, bool force_staged,
+             bool checked, int64_t stage_capacity) {
   TORCH_CHECK(heap.peers_open(), "symmetric heap: peers are not mapped yet");
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
               "input and weight must be bf16 CUDA tensors");
@@ -441,6 +442,8 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.fuse_own = fuse_own ? 1 : 0;
   g.tma_store = tma_store ? 1 : 0;
   g.force_staged = force_staged ? 1 : 0;
+  g.checked = checked ? 1 : 0;
+  g.stage_capacity = (uint64_t)stage_capacity;
   if (trace.has_value() && trace->defined()) {
     TORCH_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 8 * 160,
                 "trace must be a contiguous int64 tensor with at least 1280 elements");

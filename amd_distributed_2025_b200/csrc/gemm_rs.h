@@ -13,7 +13,9 @@
 //     that owner's arrival counters -- tiles are visited so that the rows a rank owns
 //     itself come last;
 //   * reduces the world_size partials of its own rows in fixed rank order in fp32, adds the
-//     bias with its multiplicity, rounds once and writes out[M/ws, N].
+//     bias with its multiplicity, rounds once and writes out[M/ws, N] -- on dedicated reducer
+//     warps that take each output unit as soon as its last partial has arrived, while the
+//     tensor cores are still busy with other tiles.
 // Small problems are cut along K into slices that travel as fp32 "virtual ranks".
 #pragma once
 #include <cuda_runtime.h>
@@ -55,6 +57,8 @@ struct GemmRsArgs {
                     // staged like the others and reduced by all CTAs after the GEMM tiles
   int tma_store;    // 0 = per-lane staging stores only; otherwise TMA stores where the shape allows
   int force_staged; // 1 = stage and reduce even on a single rank (exercises the staged path on one GPU)
+  int checked;      // 1 = range-check every staging store against `stage_capacity` (record and skip on violation)
+  uint64_t stage_capacity;  // bytes of one parity's staging region
 };
 
 // How a problem will be run, and what ONE parity of its workspace needs.  A pure function of

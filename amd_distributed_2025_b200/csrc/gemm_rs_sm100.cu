@@ -15,10 +15,15 @@
 //                 256-byte row segments (direct output, mixed-ownership tiles, fp32 slices)
 //   warp 6        signaller: after a tile's rows are stored, fences once and bumps the
 //                 owners' arrival counters, keeping that latency off the epilogue warps
+//   warps 7..10   reducers: from the start of the kernel they take this rank's staged output
+//                 units (a 32-row quarter of a tile, or a whole tile) in the order in which
+//                 they complete, wait (bounded) until all partials of a unit have arrived, add
+//                 them in rank order in fp32 and write the result -- while the other warps,
+//                 and the other SMs, still multiply.  When a CTA's GEMM tiles are done its
+//                 seven other warps join them.
 // A rank's own rows are finished either in the epilogue of its own tiles (peers' staged rows
-// added there) or, by default beyond 4 ranks, in a reduction pass that every CTA joins after
-// its share of GEMM tiles; tiles that straddle an ownership boundary and K-sliced problems
-// always take the pass.
+// added there; default up to 4 ranks) or by the reducers; tiles that straddle an ownership
+// boundary and K-sliced problems always go to the reducers.
 //
 // Staging buffers and counters exist in two parities that calls alternate between.  A rank
 // reaches call n+2 only after it received every peer's partials of call n+1, so every peer
@@ -45,7 +50,9 @@ namespace {
 constexpr int BM = kGemmRsBlockM;  // 128: one TMEM lane per output row
 constexpr int BK = kGemmRsBlockK;  // 64 bf16 = one 128-byte swizzled row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 224;  // producer, MMA issuer, 4 epilogue warps, signaller
+constexpr int kMainThreads = 224;  // producer, MMA issuer, 4 epilogue warps, signaller
+constexpr int kReducerWarps = 4;
+constexpr int kThreads = kMainThreads + 32 * kReducerWarps;
 constexpr int kEpilogueWarps = 4;
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in maximum per CTA
 
@@ -105,6 +112,9 @@ struct KernelParams {
   int direct;       // 1: one rank, K not sliced: tiles are written straight to `out`, nothing is staged
   int tma_store;    // 1: whole 32-row groups go to one owner and there are tensor maps for every owner:
                     // staged tiles leave through TMA stores instead of per-lane stores
+  int checked;      // 1: every staging store first proves that its owner and byte range lie inside the
+                    // staging region of one parity; a violation is recorded (STATUS_BAD_INDEX) and skipped
+  uint64_t stage_capacity;  // bytes of one parity's staging region
 };
 
 constexpr int kMaxStageMaps = 8;
@@ -243,20 +253,23 @@ __device__ __forceinline__ void reduce_partials2(const KernelParams& p, const __
   }
 }
 
-// Reduce `items` 16-byte vectors of the block rows [r0, ...) x columns [c0, c0 + 8 * vec_per_row)
-// with the whole CTA.  Every thread keeps 8 vectors per source in flight (the reduction is
-// latency-bound otherwise), adds sources in (virtual) rank order in fp32, rounds once.
+// One warp reduces `items` 16-byte output vectors of the block rows [r0, ...) x columns
+// [c0, c0 + 8 * vec_per_row).  Every lane keeps 4 vectors of 4 sources in flight (the
+// reduction is latency-bound otherwise), adds sources in (virtual) rank order in fp32 and
+// rounds once.
 __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_bfloat16* stage, int r0, int row_lo,
-                                             int c0, int vec_per_row, int items, int tid) {
-  constexpr int U = 8;
+                                             int c0, int vec_per_row, int items, int lane) {
+  constexpr int U = 4;
+  constexpr int S = 4;
   const size_t R = (size_t)p.rows_per_rank;
+  const size_t src_stride = R * p.N;
   const int sources = p.world_size * p.splits;
-  for (int base = tid; base < items; base += kThreads * U) {
+  for (int base = lane; base < items; base += 32 * U) {
     float acc[U][8];
     size_t off[U];  // element offset of the vector inside one source's [R, N] block; ~0 = past the end
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int i = base + u * kThreads;
+      const int i = base + u * 32;
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
       if (i < items) {
@@ -267,28 +280,29 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
         off[u] = ~(size_t)0;
       }
     }
-    // two sources per step: 16 loads in flight per thread, added in rank order
-    for (int s = 0; s < sources; s += 2) {
-      const __nv_bfloat16* src0 = stage + (size_t)s * R * p.N;
-      const __nv_bfloat16* src1 = src0 + R * p.N;
-      const bool two = s + 1 < sources;
-      uint4 v0[U], v1[U];
+    for (int s = 0; s < sources; s += S) {
+      uint4 v[S][U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const bool live = off[u] != ~(size_t)0;
-        v0[u] = live ? __ldcg(reinterpret_cast<const uint4*>(src0 + off[u])) : make_uint4(0, 0, 0, 0);
-        v1[u] = (live && two) ? __ldcg(reinterpret_cast<const uint4*>(src1 + off[u])) : make_uint4(0, 0, 0, 0);
+      for (int q = 0; q < S; ++q) {
+        const bool have = s + q < sources;
+        const __nv_bfloat16* src = stage + (size_t)(s + q) * src_stride;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          v[q][u] = (have && off[u] != ~(size_t)0) ? __ldcg(reinterpret_cast<const uint4*>(src + off[u]))
+                                                   : make_uint4(0, 0, 0, 0);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[u]);
-        const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[u]);
+      for (int q = 0; q < S; ++q) {  // ascending (virtual) rank
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f0 = __bfloat1622float2(h0[e]);
-          const float2 f1 = __bfloat1622float2(h1[e]);
-          acc[u][2 * e] = (acc[u][2 * e] + f0.x) + f1.x;
-          acc[u][2 * e + 1] = (acc[u][2 * e + 1] + f0.y) + f1.y;
+        for (int u = 0; u < U; ++u) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[q][u]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            acc[u][2 * e] += f.x;
+            acc[u][2 * e + 1] += f.y;
+          }
         }
       }
     }
@@ -321,16 +335,16 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
 // output in the reference -- the bias is added per rank in bf16 if the reference order was
 // asked for, and the ranks are then summed in fp32 and rounded once.
 __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const float* stage, int r0, int row_lo,
-                                                    int c0, int vec_per_row, int items, int tid) {
-  constexpr int U = 4;
+                                                    int c0, int vec_per_row, int items, int lane) {
+  constexpr int U = 2;
   const size_t R = (size_t)p.rows_per_rank;
-  for (int base = tid; base < items; base += kThreads * U) {
+  for (int base = lane; base < items; base += 32 * U) {
     float acc[U][8];
     size_t off[U];
     float bias_f[U][8];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int i = base + u * kThreads;
+      const int i = base + u * 32;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         acc[u][e] = 0.f;
@@ -359,29 +373,29 @@ __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int e = 0; e < 8; ++e) part[u][e] = 0.f;
-      for (int sl = 0; sl < p.splits; ++sl) {
-        const float* src = stage + (size_t)(r * p.splits + sl) * R * p.N;
-        uint4 lo[U], hi[U];
+      for (int sl = 0; sl < p.splits; sl += 2) {
+        const float* src0 = stage + (size_t)(r * p.splits + sl) * R * p.N;
+        const float* src1 = src0 + R * p.N;
+        const bool two = sl + 1 < p.splits;
+        uint4 lo0[U], hi0[U], lo1[U], hi1[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (off[u] != ~(size_t)0) {
-            lo[u] = __ldcg(reinterpret_cast<const uint4*>(src + off[u]));
-            hi[u] = __ldcg(reinterpret_cast<const uint4*>(src + off[u] + 4));
-          } else {
-            lo[u] = make_uint4(0, 0, 0, 0);
-            hi[u] = make_uint4(0, 0, 0, 0);
-          }
+          const bool live = off[u] != ~(size_t)0;
+          lo0[u] = live ? __ldcg(reinterpret_cast<const uint4*>(src0 + off[u])) : make_uint4(0, 0, 0, 0);
+          hi0[u] = live ? __ldcg(reinterpret_cast<const uint4*>(src0 + off[u] + 4)) : make_uint4(0, 0, 0, 0);
+          lo1[u] = (live && two) ? __ldcg(reinterpret_cast<const uint4*>(src1 + off[u])) : make_uint4(0, 0, 0, 0);
+          hi1[u] = (live && two) ? __ldcg(reinterpret_cast<const uint4*>(src1 + off[u] + 4)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          part[u][0] += __uint_as_float(lo[u].x);
-          part[u][1] += __uint_as_float(lo[u].y);
-          part[u][2] += __uint_as_float(lo[u].z);
-          part[u][3] += __uint_as_float(lo[u].w);
-          part[u][4] += __uint_as_float(hi[u].x);
-          part[u][5] += __uint_as_float(hi[u].y);
-          part[u][6] += __uint_as_float(hi[u].z);
-          part[u][7] += __uint_as_float(hi[u].w);
+          part[u][0] = (part[u][0] + __uint_as_float(lo0[u].x)) + __uint_as_float(lo1[u].x);
+          part[u][1] = (part[u][1] + __uint_as_float(lo0[u].y)) + __uint_as_float(lo1[u].y);
+          part[u][2] = (part[u][2] + __uint_as_float(lo0[u].z)) + __uint_as_float(lo1[u].z);
+          part[u][3] = (part[u][3] + __uint_as_float(lo0[u].w)) + __uint_as_float(lo1[u].w);
+          part[u][4] = (part[u][4] + __uint_as_float(hi0[u].x)) + __uint_as_float(hi1[u].x);
+          part[u][5] = (part[u][5] + __uint_as_float(hi0[u].y)) + __uint_as_float(hi1[u].y);
+          part[u][6] = (part[u][6] + __uint_as_float(hi0[u].z)) + __uint_as_float(hi1[u].z);
+          part[u][7] = (part[u][7] + __uint_as_float(hi0[u].w)) + __uint_as_float(hi1[u].w);
         }
       }
 #pragma unroll
@@ -411,6 +425,91 @@ __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const
   }
 }
 
+// The reduction of this rank's staged output, shared by the reducer warps (from the start of
+// the kernel) and by the other warps (once their GEMM tiles are done).  Units are numbered in
+// the order in which they complete -- column tile by column tile over the rank's row blocks,
+// as the tile schedule visits them -- and dealt to the CTAs round robin; inside a CTA a
+// shared counter hands the next unit to whichever warp asks, and that warp waits (bounded)
+// for the unit's arrival counters before it reduces.  Tiles that straddle an ownership
+// boundary (always the case when a rank owns fewer than 128 rows) and all tiles of a K-sliced
+// problem were staged by every (virtual) rank, this one included.
+template <int BN>
+__device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* next_unit, volatile int* abort, int lane) {
+  const int G = gridDim.x;
+  const int R = p.rows_per_rank;
+  const int row_lo = p.rank * R;
+  const int mb_lo = row_lo / BM;
+  const int mb_hi = (row_lo + R - 1) / BM;
+  // staged row blocks: all of [mb_lo, mb_hi], or only its (at most two) partly owned ends
+  const bool lo_staged = !tile_owned(p, mb_lo);
+  const bool hi_staged = mb_hi != mb_lo && !tile_owned(p, mb_hi);
+  const bool all_staged = !(p.fuse_own && p.splits == 1);
+  const int n_mb = all_staged ? (mb_hi - mb_lo + 1) : ((lo_staged ? 1 : 0) + (hi_staged ? 1 : 0));
+  if (n_mb == 0) return;
+  // Unit of work: a whole 128 x BN tile (four counters) when there are plenty of tiles, else one
+  // 32-row quarter of a tile (one counter) so that a small problem still occupies every CTA.
+  const int parts = (n_mb * p.n_tiles >= 2 * G) ? 1 : kEpilogueWarps;
+  const int rows_per_part = BM / parts;
+  const int ctrs_per_part = kEpilogueWarps / parts;
+  const int total_units = p.n_tiles * n_mb * parts;
+  const uint32_t want = (uint32_t)(p.world_size * p.splits);
+  uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
+  const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
+  const int first = G - 1 - (int)blockIdx.x;  // CTAs with fewer GEMM tiles get the earlier units
+  while (!*abort) {
+    int li = 0;
+    if (lane == 0) li = atomicAdd(next_unit, 1);
+    li = __shfl_sync(0xffffffffu, li, 0);
+    const long long j = (long long)first + (long long)li * G;
+    if (j >= total_units) break;
+    const int part = (int)(j % parts);
+    const int rest = (int)(j / parts);
+    const int mi = rest % n_mb;
+    const int nb = rest / n_mb;
+    const int mb = all_staged ? mb_lo + mi : ((mi == 0 && lo_staged) ? mb_lo : mb_hi);
+    uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps + part * ctrs_per_part;
+    int ok = 1;
+    if (lane < ctrs_per_part) {
+      // long sleeps: this wait can last for most of the kernel and must not steal issue slots
+      // from the warps that feed the tensor cores
+      const uint32_t* c = ctr + lane;
+      const bool sys = p.world_size > 1;
+      uint32_t seen = sys ? ld_acquire_sys_u32(c) : ld_acquire_gpu_u32(c);
+      if (seen < want) {
+        const uint64_t t0 = global_timer_ns();
+        while (true) {
+          __nanosleep(400);
+          seen = sys ? ld_acquire_sys_u32(c) : ld_acquire_gpu_u32(c);
+          if (seen >= want) break;
+          if (*abort || global_timer_ns() - t0 > p.timeout_ns) {
+            if (!*abort) record_status(p.status, STATUS_TIMEOUT, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb, want, seen);
+            *abort = 1;
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const int r0 = max(mb * BM + part * rows_per_part, row_lo);
+    const int r1 = min(min(mb * BM + (part + 1) * rows_per_part, row_lo + R), p.M);
+    if (r1 > r0) {
+      const int c0 = nb * BN;
+      const int c1 = min(c0 + BN, p.N);
+      const int vec_per_row = (c1 - c0) >> 3;
+      if (p.splits > 1) {
+        reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
+                            (r1 - r0) * vec_per_row, lane);
+      } else {
+        reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, lane);
+      }
+    }
+    __syncwarp();
+    if (lane < ctrs_per_part) ctr[lane] = 0;  // this parity's counters are next used two calls from now
+  }
+}
+
 }  // namespace
 
 template <int BN, int CTAS>
@@ -421,7 +520,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_flag;
   __shared__ uint32_t tmem_base_shared;
-  __shared__ int wait_ok_shared;
+  __shared__ int next_unit_shared;  // next reduction unit of this CTA to hand out
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -443,6 +542,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   if (tid == 0) {
     abort_flag = 0;
+    next_unit_shared = 0;
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);   // one arrive (with the byte count) per phase, by the leader's producer
       ptx::mbar_init(empty_bar(s), 1);  // one commit per phase, by the MMA issuer (to both CTAs of a pair)
@@ -683,7 +783,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           // ---- slab -> owner's staging block, one TMA box per 64 columns -------------------
           ptx::fence_proxy_async_smem();  // this lane's slab writes, for the async proxy
           __syncwarp();
-          if (lane == 0 && p.debug != 2) {
+          bool in_range = true;
+          if (p.checked) {
+            const long long rl0 = (long long)m0 - (long long)owner0 * R;
+            in_range = owner0 >= 0 && owner0 < p.world_size && rl0 >= 0 && rl0 + 32 <= R &&
+                       ((uint64_t)(p.rank + 1) * R * p.N * 2ull) <= p.stage_capacity;
+            if (!in_range && lane == 0)
+              record_status(p.status, STATUS_BAD_INDEX, PHASE_RS_PARTIALS, owner0, (int)(mb * p.n_tiles + nb), p.epoch, (uint64_t)m0);
+          }
+          if (lane == 0 && p.debug != 2 && in_range) {
             const void* map = &stage_maps.m[p.debug == 1 ? p.rank : owner0];
 #pragma unroll
             for (int sub = 0; sub < C::kEpiCols / 64; ++sub) {
@@ -740,6 +848,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const int m = m0 + rr;
           const int n = n0 + half * cols_per_pass + cc * (sliced ? 4 : 8);
           if (m < p.M && n < p.N) {
+            if (p.checked && !direct) {
+              const int owner = m / R;
+              const uint64_t elem = ((uint64_t)(p.rank * p.splits + split) * R + (uint64_t)(m - owner * R)) * p.N + n;
+              const uint64_t end = sliced ? (elem + 4) * 4ull : (elem + 8) * 2ull;
+              if (owner >= p.world_size || end > p.stage_capacity) {
+                record_status(p.status, STATUS_BAD_INDEX, PHASE_RS_PARTIALS, owner, (int)(mb * p.n_tiles + nb), p.epoch, end);
+                continue;
+              }
+            }
             if (sliced) {
               const int owner = m / R;
               const int rl = m - owner * R;
@@ -814,14 +931,27 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         ptx::mbar_arrive(sempty_bar(acc));
       }
     }
+  } else {
+    // ================================ reducers ==========================================
+    if (!p.direct) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane);
   }
 
-  // ================================ teardown of the GEMM phase ===========================
-  if (abort_flag) {
-    // give copies still in flight time to land before shared memory is released
-    const uint64_t t0 = global_timer_ns();
-    while (global_timer_ns() - t0 < 200000) __nanosleep(1000);
+  // ================================ end of the GEMM phase ================================
+  if (warp < kMainThreads / 32) {
+    if (abort_flag) {
+      // give copies still in flight time to land before shared memory is released
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000) __nanosleep(1000);
+    }
+    // the seven GEMM warps meet among themselves (the reducers are still at work) ...
+    __syncwarp();
+    asm volatile("bar.sync 1, %0;" ::"n"(kMainThreads) : "memory");
+    trace_stamp(p, 2);
+    // ... and help with what is left of the reduction
+    if (!p.direct && !abort_flag) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane);
   }
+
+  // ================================ teardown =============================================
   ptx::tcgen05_fence_before();
   __syncthreads();
   // A CTA of a pair must not retire while its partner may still signal its barriers or
@@ -832,67 +962,6 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     __syncwarp();
     if (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
     else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
-  }
-  trace_stamp(p, 2);
-  if (p.direct || abort_flag) {
-    trace_stamp(p, 3);
-    return;
-  }
-
-  // ================================ reduction of staged tiles =============================
-  // Tiles that straddle an ownership boundary (always the case when a rank owns fewer than
-  // 128 rows) and all tiles of a K-sliced problem were staged by every (virtual) rank, this
-  // one included.  Unit j is reduced by CTA (G-1 - j % G) so that CTAs with fewer GEMM tiles
-  // start first.
-  const int R = p.rows_per_rank;
-  const int row_lo = p.rank * R;
-  const int mb_lo = row_lo / BM;
-  const int mb_hi = (row_lo + R - 1) / BM;
-  const uint32_t want = (uint32_t)(p.world_size * p.splits);
-  uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
-  const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
-  // Unit of work: a whole 128 x BN tile (four counters) when there are plenty of tiles, else one
-  // 32-row quarter of a tile (one counter) so that a small problem still occupies every CTA.
-  int staged_tiles = 0;
-  for (int mb = mb_lo; mb <= mb_hi; ++mb)
-    if (!tile_owned(p, mb)) staged_tiles += p.n_tiles;
-  const int parts = (staged_tiles >= 2 * G) ? 1 : kEpilogueWarps;  // units per tile
-  const int rows_per_part = BM / parts;
-  const int ctrs_per_part = kEpilogueWarps / parts;
-  int j = 0;
-  for (int mb = mb_lo; mb <= mb_hi; ++mb) {
-    if (tile_owned(p, mb)) continue;
-    for (int nb = 0; nb < p.n_tiles; ++nb) {
-      for (int part = 0; part < parts; ++part, ++j) {
-        if (j % G != G - 1 - (int)blockIdx.x) continue;
-        const int r0 = max(mb * BM + part * rows_per_part, row_lo);
-        const int r1 = min(min(mb * BM + (part + 1) * rows_per_part, row_lo + R), p.M);
-        uint32_t* ctr = counters + ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps + part * ctrs_per_part;
-        if (tid == 0) wait_ok_shared = 1;
-        __syncthreads();
-        if (tid < ctrs_per_part) {
-          if (!wait_u32_ge(ctr + tid, want, limit, p.status, PHASE_RS_PARTIALS, -1, mb * p.n_tiles + nb,
-                           p.world_size > 1))
-            wait_ok_shared = 0;
-        }
-        __syncthreads();
-        const bool ok = wait_ok_shared != 0;
-        if (ok && r1 > r0) {
-          const int c0 = nb * BN;
-          const int c1 = min(c0 + BN, p.N);
-          const int vec_per_row = (c1 - c0) >> 3;
-          if (p.splits > 1) {
-            reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
-                                (r1 - r0) * vec_per_row, tid);
-          } else {
-            reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, tid);
-          }
-        }
-        __syncthreads();
-        if (tid < ctrs_per_part) ctr[tid] = 0;  // this parity's counters are next used two calls from now
-        if (!ok) return;
-      }
-    }
   }
   trace_stamp(p, 3);
 }
@@ -1051,6 +1120,8 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, int splits, cudaStream_t 
   p.trace = a.trace;
   p.debug = a.debug;
   p.fuse_own = a.fuse_own;
+  p.checked = a.checked;
+  p.stage_capacity = a.stage_capacity;
   p.direct = (a.world_size == 1 && splits == 1 && !a.force_staged) ? 1 : 0;
   StageMaps maps;
   std::memset(&maps, 0, sizeof(maps));

@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   // ---- phase E: every CTA has delivered -> tell the owners --------------------------------
   if (last_cta_arrives(&p.sync_counters[1])) {
     if (tid == 0) {
-      if (alive) {
+      if (!status_timed_out(p.status)) {  // no CTA of this rank gave up: everything was stored
         for (int d = 0; d < p.world_size; ++d) st_relaxed_sys(flag_ptr(p.peer_base[d], FLAG_MOE_DATA, p.rank), p.epoch);
       }
       p.sync_counters[0] = 0;
@@ -567,7 +567,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
               const int idx = v0 + lane + 32 * u;
               if (idx < v_hi) {
                 a[u] = __ldcg(s0 + idx);
-                b[u] = __ldcg(s1 + idx);
+                b[u] = two ? __ldcg(s1 + idx) : make_int4(0, 0, 0, 0);
               } else {
                 a[u] = make_int4(0, 0, 0, 0);
                 b[u] = make_int4(0, 0, 0, 0);
@@ -625,7 +625,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
   // ---- phase 2: all partial rows pushed -> tell the sources; add up what came back ----------
   if (last_cta_arrives(&p.sync_counters[3])) {
     if (tid == 0) {
-      if (alive) {
+      if (!status_timed_out(p.status)) {
         for (int d = 0; d < p.world_size; ++d) st_relaxed_sys(flag_ptr(p.peer_base[d], FLAG_MOE_RET, p.rank), p.epoch);
       }
       p.sync_counters[3] = 0;

@@ -33,6 +33,24 @@ from .. import contract, oracle
 from ..utils import timing
 
 
+def _host_time_us(fn, ws: int, iters: int = 20) -> float:
+    """Median wall time the host spends inside the call (the GPU is idle when it starts): the
+    part of a short call's event time that is Python, argument conversion and launch."""
+    import statistics
+    import time
+
+    samples = []
+    for _ in range(iters):
+        torch.cuda.synchronize()
+        if ws > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        fn()
+        samples.append((time.perf_counter() - t0) * 1e6)
+        torch.cuda.synchronize()
+    return round(statistics.median(samples), 1)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", choices=["gemm_rs", "moe", "fp8_gemm"], required=True)
@@ -40,7 +58,9 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--staged", action="store_true", help="gemm_rs: run the multi-rank staging/reduction path on one GPU")
-    ap.add_argument("--trace", action="store_true", help="gemm_rs: print the per-CTA phase stamps of the last launch")
+    ap.add_argument("--trace", action="store_true", help="print the in-kernel phase stamps of the last launch")
+    ap.add_argument("--mode", default=None, help="moe: protocol, dedup (default) or direct")
+    ap.add_argument("--routing", default="uniform", help="moe: uniform or zipf")
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=7168)
@@ -53,8 +73,8 @@ def main(argv=None) -> int:
     rank, ws = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if ws > 1:
-        if args.kernel != "gemm_rs":
-            raise SystemExit("only the gemm_rs case runs on several ranks")
+        if args.kernel == "fp8_gemm":
+            raise SystemExit("the fp8_gemm case runs on one rank")
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     out = {"kernel": args.kernel, "rank": rank, "world_size": ws}
     if args.kernel == "gemm_rs":
@@ -70,6 +90,7 @@ def main(argv=None) -> int:
         times = timing.time_cuda(lambda: op(a, w, bias), warmup=3 if ws > 1 else 1, iters=args.iters,
                                  barrier=dist.barrier if ws > 1 else None)
         op.check()
+        out["host_us"] = _host_time_us(lambda: gemm_rs.custom_kernel((a, w, bias)), ws)
         if args.trace:
             op.trace.zero_()
         y = op(a, w, bias)
@@ -95,15 +116,28 @@ def main(argv=None) -> int:
     elif args.kernel == "moe":
         from ..models import moe_all2all
 
-        cfg, data, _, _ = contract.make_moe_inputs(args.experts, args.topk, args.hidden, args.tokens, 1, 0, 1, device="cuda",
+        cfg, data, _, _ = contract.make_moe_inputs(args.experts, args.topk, args.hidden, args.tokens, 1, rank, ws, device="cuda",
                                                    dtype=getattr(torch, args.dtype), fixed_num_tokens=args.tokens,
-                                                   weights="softmax")
-        fn = lambda: moe_all2all.custom_kernel((cfg, data, 0, 1))  # noqa: E731
-        times = timing.time_cuda(fn, warmup=1, iters=args.iters)
+                                                   routing=args.routing, weights="softmax")
+        fn = lambda: moe_all2all.custom_kernel((cfg, data, rank, ws), mode=args.mode)  # noqa: E731
+        times = timing.time_cuda(fn, warmup=3 if ws > 1 else 1, iters=args.iters, barrier=dist.barrier if ws > 1 else None)
+        layer = moe_all2all.get_layer(cfg, rank, ws, mode=args.mode)
+        out["host_us"] = _host_time_us(fn, ws)
+        if args.trace and layer.engine is not None:
+            layer.enable_trace(True)
         y = fn()
-        moe_all2all.get_layer(cfg, 0, 1).check()
-        ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, data, 1))
-        out.update(config=[args.experts, args.topk, args.hidden, args.tokens], us=[t * 1e3 for t in times], ok=ok, msg=msg)
+        torch.cuda.synchronize()
+        layer.check()
+        ok, msg = oracle.check_moe_output(y, oracle.moe_expected_output(cfg, data, ws))
+        out.update(config=[args.experts, args.topk, args.hidden, args.tokens], mode=layer.mode, us=[t * 1e3 for t in times],
+                   ok=ok, msg=msg)
+        if args.trace and layer.trace is not None:
+            d, c = layer.trace[0].tolist(), layer.trace[1].tolist()
+            names_d = ["start", "counted", "rows_issued", "counts_arrived", "metadata_stored", "all_sources_delivered",
+                       "replicated", "last_cta_exit"]
+            names_c = ["start", "weights_exchanged", "partials_pushed", "all_partials_arrived", "-", "-", "-", "last_cta_exit"]
+            out["dispatch_trace_us"] = {nm: round((v - d[0]) / 1e3, 1) for nm, v in zip(names_d, d) if v > 0}
+            out["combine_trace_us"] = {nm: round((v - d[0]) / 1e3, 1) for nm, v in zip(names_c, c) if v > 0 and nm != "-"}
     else:
         from ..ops.fp8_gemm import fp8_gemm, fp8_gemm_reference
 

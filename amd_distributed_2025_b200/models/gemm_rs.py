@@ -149,6 +149,8 @@ class GemmRS:
             (self.world_size <= 4) if self.fuse_own is None else bool(self.fuse_own),
             self.tma_store,
             self.force_staged,
+            self.checked,
+            self.stage_bytes,
         )
         return out
 

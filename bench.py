@@ -121,10 +121,12 @@ def build_inputs(rank: int, ws: int, device: torch.device):
 # --------------------------------------------------------------------------------------
 class Ours:
     name = "ours"
-    kernels_per_call = {"moe": 2, "gemm_rs": 1}  # dispatch (with the expert op) + combine; fused GEMM-RS
-
     def __init__(self, rank: int, ws: int):
         from amd_distributed_2025_b200.models import gemm_rs, moe_all2all
+
+        # "dedup": dispatch (with the expert op) + combine; "direct": dispatch + expert scale + combine;
+        # the fused GEMM-RS is one launch
+        self.kernels_per_call = {"moe": 2 if moe_all2all.default_mode() == "dedup" else 3, "gemm_rs": 1}
 
         self.rank, self.ws = rank, ws
         self.moe, self.gemm = moe_all2all, gemm_rs
