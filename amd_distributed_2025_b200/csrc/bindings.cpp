@@ -244,8 +244,11 @@ class MoeDedupEngine {
     trace_c_ = check_trace(combine_trace);
   }
 
-  void dispatch(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
-                bool fuse_scale, double scale) {
+  // dispatch / combine / forward return 0 after launching, or the code of a failure that an earlier
+  // kernel recorded (nothing is launched then; the caller turns the record into an exception).
+  int dispatch(const at::Tensor& x, const at::Tensor& indices, const c10::optional<at::Tensor>& weights,
+               bool fuse_scale, double scale) {
+    if (const uint32_t code = heap_->status_host().code) return (int)code;
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == dtype_ && x.size(1) == H_,
                 "x must be a contiguous [T, hidden] CUDA tensor of the layer's dtype");
     TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() && indices.scalar_type() == at::kInt &&
@@ -300,9 +303,11 @@ class MoeDedupEngine {
     weights_sent_ = wptr != nullptr;
     num_tokens_ = (int)T;
     cuda_check(b200::launch_moe_dedup_dispatch(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dedup_dispatch launch");
+    return 0;
   }
 
-  void combine(at::Tensor out, const at::Tensor& weights, const c10::optional<at::Tensor>& expert_y) {
+  int combine(at::Tensor out, const at::Tensor& weights, const c10::optional<at::Tensor>& expert_y) {
+    if (const uint32_t code = heap_->status_host().code) return (int)code;
     const int64_t T = num_tokens_;
     TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.is_contiguous() && out.scalar_type() == dtype_ &&
                     out.size(0) >= T && out.size(1) == H_,
@@ -347,12 +352,13 @@ class MoeDedupEngine {
     const int64_t want = ((int64_t)ws * std::max<int64_t>(T, 1) * p.pieces + 7) / 8;
     const int grid = (int)std::max<int64_t>(std::min<int64_t>(combine_blocks_, want), 1);
     cuda_check(b200::launch_moe_dedup_combine(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dedup_combine launch");
+    return 0;
   }
 
   // dispatch (carrying the weights, applying expert_y = expert_x * scale on the way) + combine
-  void forward(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& weights, at::Tensor out, double scale) {
-    dispatch(x, indices, weights, true, scale);
-    combine(out, weights, c10::nullopt);
+  int forward(const at::Tensor& x, const at::Tensor& indices, const at::Tensor& weights, at::Tensor out, double scale) {
+    if (const int rc = dispatch(x, indices, weights, true, scale)) return rc;
+    return combine(out, weights, c10::nullopt);
   }
 
  private:
@@ -451,6 +457,136 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   }
   cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
 }
+
+
+// One object per GEMM-RS workspace: offsets of both parities, the call number and the knobs
+// live here, so a call converts four tensors, looks its plan up and launches.
+class GemmRsEngine {
+ public:
+  GemmRsEngine(std::shared_ptr<SymmHeap> heap, std::vector<int64_t> stage_offsets, std::vector<int64_t> counter_offsets,
+               int64_t stage_bytes, int64_t counter_bytes, int64_t timeout_ns)
+      : heap_(std::move(heap)), stage_bytes_(stage_bytes), counter_bytes_(counter_bytes), timeout_ns_(timeout_ns) {
+    TORCH_CHECK(stage_offsets.size() == 2 && counter_offsets.size() == 2, "two parities of staging and counters");
+    for (int i = 0; i < 2; ++i) {
+      off_stage_[i] = (uint64_t)stage_offsets[i];
+      off_counters_[i] = (uint64_t)counter_offsets[i];
+    }
+  }
+
+  // knobs (0 / -1 = chosen from the shape); see GemmRsArgs
+  int64_t max_ctas = 0, block_n = 0, cta_pair = -1, splits = 0, debug = 0;
+  int64_t fuse_own = -1;  // -1: fused up to 4 ranks
+  bool tma_store = true, force_staged = false, checked = false;
+
+  int64_t epoch() const { return epoch_; }
+  void restart_epochs() { epoch_ = 0; }
+  void set_trace(const c10::optional<at::Tensor>& trace) {
+    trace_ = nullptr;
+    trace_keep_ = at::Tensor();
+    if (trace.has_value() && trace->defined()) {
+      TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 8 * 160,
+                  "trace must be a contiguous int64 CUDA tensor with at least 1280 elements");
+      trace_keep_ = *trace;
+      trace_ = reinterpret_cast<uint64_t*>(trace->data_ptr<int64_t>());
+    }
+  }
+
+  py::dict plan(int64_t M, int64_t N, int64_t K) {
+    c10::cuda::CUDAGuard guard(heap_->device());
+    const b200::GemmRsPlan p = b200::gemm_rs_plan((int)M, (int)N, (int)K, heap_->world_size(), (int)block_n, (int)cta_pair, (int)splits);
+    py::dict d;
+    d["block_n"] = p.block_n;
+    d["cta_pair"] = p.cta_pair;
+    d["splits"] = p.splits;
+    d["stage_bytes"] = (int64_t)p.stage_bytes;
+    d["counter_bytes"] = (int64_t)p.counter_bytes;
+    return d;
+  }
+
+  // Returns 0 after a launch, or the code of a failure that an earlier kernel recorded (nothing is
+  // launched then; the caller turns the record into an exception).
+  int run(const at::Tensor& a, const at::Tensor& w, const c10::optional<at::Tensor>& bias, at::Tensor out,
+          bool bias_at_source, double bias_scale) {
+    TORCH_CHECK(heap_->peers_open(), "symmetric heap: peers are not mapped yet");
+    if (const uint32_t code = heap_->status_host().code) return (int)code;
+    TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16,
+                "input and weight must be bf16 CUDA tensors");
+    TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "input [M, K] and weight [N, K] disagree on K");
+    TORCH_CHECK(a.is_contiguous() && w.is_contiguous() && out.is_contiguous(), "operands must be contiguous");
+    const int ws = heap_->world_size();
+    const int64_t M = a.size(0), N = w.size(0), K = a.size(1);
+    TORCH_CHECK(M % ws == 0, "M must be divisible by world_size");
+    TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == M / ws && out.size(1) == N, "out must be bf16 [M/ws, N]");
+    TORCH_CHECK(K % 8 == 0, "K per rank must be a multiple of 8 (16-byte rows for TMA)");
+    TORCH_CHECK(N % 8 == 0, "N must be a multiple of 8 (16-byte vector epilogue)");
+    const void* bias_ptr = nullptr;
+    if (bias.has_value() && bias->defined()) {
+      TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "bias must be bf16 [N]");
+      bias_ptr = bias->data_ptr();
+    }
+    c10::cuda::CUDAGuard guard(heap_->device());
+    const b200::GemmRsPlan plan = cached_plan((int)M, (int)N, (int)K);
+    TORCH_CHECK((int64_t)plan.stage_bytes <= stage_bytes_ && (int64_t)plan.counter_bytes <= counter_bytes_, "problem ", M, "x",
+                N, "x", K, " needs ", plan.stage_bytes, " staging bytes, the workspace has ", stage_bytes_);
+    b200::GemmRsArgs g;
+    g.a = a.data_ptr();
+    g.w = w.data_ptr();
+    g.bias = bias_ptr;
+    g.out = out.data_ptr();
+    g.M = (int)M;
+    g.N = (int)N;
+    g.K = (int)K;
+    g.world_size = ws;
+    g.rank = heap_->rank();
+    g.bias_scale = (float)bias_scale;
+    g.bias_at_source = bias_at_source ? 1 : 0;
+    fill_peer_bases(*heap_, g.peer_base);
+    const int64_t epoch = ++epoch_;
+    const int parity = (int)(epoch & 1);
+    g.off_stage = off_stage_[parity];
+    g.off_counters = off_counters_[parity];
+    g.epoch = (uint64_t)epoch;
+    g.timeout_ns = (uint64_t)timeout_ns_;
+    g.status = heap_->status_device();
+    g.sync_counters = heap_->sync_counters() + 8;
+    g.max_ctas = (int)max_ctas;
+    g.block_n = plan.block_n;
+    g.cta_pair = plan.cta_pair;
+    g.splits = plan.splits;
+    g.trace = trace_;
+    g.debug = (int)debug;
+    g.fuse_own = fuse_own < 0 ? (ws <= 4 ? 1 : 0) : (fuse_own != 0 ? 1 : 0);
+    g.tma_store = tma_store ? 1 : 0;
+    g.force_staged = force_staged ? 1 : 0;
+    g.checked = checked ? 1 : 0;
+    g.stage_capacity = (uint64_t)stage_bytes_;
+    cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
+    return 0;
+  }
+
+ private:
+  b200::GemmRsPlan cached_plan(int M, int N, int K) {
+    for (const auto& e : plans_)
+      if (e.M == M && e.N == N && e.K == K && e.block_n == block_n && e.cta_pair == cta_pair && e.splits == splits) return e.plan;
+    PlanEntry e{M, N, K, block_n, cta_pair, splits,
+                b200::gemm_rs_plan(M, N, K, heap_->world_size(), (int)block_n, (int)cta_pair, (int)splits)};
+    if (plans_.size() >= 32) plans_.erase(plans_.begin());
+    plans_.push_back(e);
+    return e.plan;
+  }
+  struct PlanEntry {
+    int M, N, K;
+    int64_t block_n, cta_pair, splits;
+    b200::GemmRsPlan plan;
+  };
+  std::shared_ptr<SymmHeap> heap_;
+  uint64_t off_stage_[2], off_counters_[2];
+  int64_t stage_bytes_, counter_bytes_, timeout_ns_;
+  int64_t epoch_ = 0;
+  uint64_t* trace_ = nullptr;
+  at::Tensor trace_keep_;
+  std::vector<PlanEntry> plans_;
+};
 
 // ------------------------------------------------------------------------ fp8 GEMM ----
 
@@ -766,6 +902,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard guard(device);
     return b200::moe_dedup_dispatch_max_blocks(device, num_experts, num_entries);
   });
+
+  py::class_<GemmRsEngine, std::shared_ptr<GemmRsEngine>>(m, "GemmRsEngine")
+      .def(py::init<std::shared_ptr<SymmHeap>, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, int64_t>(),
+           py::arg("heap"), py::arg("stage_offsets"), py::arg("counter_offsets"), py::arg("stage_bytes"),
+           py::arg("counter_bytes"), py::arg("timeout_ns"))
+      .def("run", &GemmRsEngine::run, py::arg("a"), py::arg("w"), py::arg("bias"), py::arg("out"),
+           py::arg("bias_at_source") = true, py::arg("bias_scale") = 1.0)
+      .def("plan", &GemmRsEngine::plan)
+      .def("set_trace", &GemmRsEngine::set_trace)
+      .def("restart_epochs", &GemmRsEngine::restart_epochs)
+      .def_property_readonly("epoch", &GemmRsEngine::epoch)
+      .def_readwrite("max_ctas", &GemmRsEngine::max_ctas)
+      .def_readwrite("block_n", &GemmRsEngine::block_n)
+      .def_readwrite("cta_pair", &GemmRsEngine::cta_pair)
+      .def_readwrite("splits", &GemmRsEngine::splits)
+      .def_readwrite("debug", &GemmRsEngine::debug)
+      .def_readwrite("fuse_own", &GemmRsEngine::fuse_own)
+      .def_readwrite("tma_store", &GemmRsEngine::tma_store)
+      .def_readwrite("force_staged", &GemmRsEngine::force_staged)
+      .def_readwrite("checked", &GemmRsEngine::checked);
 
   m.attr("FLAG_BARRIER") = (int)b200::FLAG_BARRIER;
   m.attr("FLAG_TEST") = (int)b200::FLAG_TEST;

@@ -253,18 +253,18 @@ __device__ __forceinline__ void reduce_partials2(const KernelParams& p, const __
   }
 }
 
-// One warp reduces `items` 16-byte output vectors of the block rows [r0, ...) x columns
-// [c0, c0 + 8 * vec_per_row).  Every lane keeps 4 vectors of 4 sources in flight (the
+// One warp reduces the 16-byte output vectors [item_lo, items) of the block rows [r0, ...) x
+// columns [c0, c0 + 8 * vec_per_row) (vectors numbered row by row).  Every lane keeps 4 vectors of 4 sources in flight (the
 // reduction is latency-bound otherwise), adds sources in (virtual) rank order in fp32 and
 // rounds once.
 __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_bfloat16* stage, int r0, int row_lo,
-                                             int c0, int vec_per_row, int items, int lane) {
+                                             int c0, int vec_per_row, int item_lo, int items, int lane) {
   constexpr int U = 4;
   constexpr int S = 4;
   const size_t R = (size_t)p.rows_per_rank;
   const size_t src_stride = R * p.N;
   const int sources = p.world_size * p.splits;
-  for (int base = lane; base < items; base += 32 * U) {
+  for (int base = item_lo + lane; base < items; base += 32 * U) {
     float acc[U][8];
     size_t off[U];  // element offset of the vector inside one source's [R, N] block; ~0 = past the end
 #pragma unroll
@@ -335,10 +335,10 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
 // output in the reference -- the bias is added per rank in bf16 if the reference order was
 // asked for, and the ranks are then summed in fp32 and rounded once.
 __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const float* stage, int r0, int row_lo,
-                                                    int c0, int vec_per_row, int items, int lane) {
+                                                    int c0, int vec_per_row, int item_lo, int items, int lane) {
   constexpr int U = 2;
   const size_t R = (size_t)p.rows_per_rank;
-  for (int base = lane; base < items; base += 32 * U) {
+  for (int base = item_lo + lane; base < items; base += 32 * U) {
     float acc[U][8];
     size_t off[U];
     float bias_f[U][8];
@@ -452,6 +452,14 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
   const int rows_per_part = BM / parts;
   const int ctrs_per_part = kEpilogueWarps / parts;
   const int total_units = p.n_tiles * n_mb * parts;
+  // A unit is cut further into `cuts` runs of its output vectors when there are fewer units than
+  // warps: one warp on a whole unit is a long chain of dependent loads, and the last units to
+  // complete decide when the kernel ends.
+  const int unit_items = rows_per_part * (BN / 8);
+  int cuts = (2 * G * (kThreads / 32) + total_units - 1) / total_units;
+  cuts = max(1, min(min(cuts, unit_items / 128), 16));
+  const int cut_items = (unit_items + cuts - 1) / cuts;
+  const long long total_work = (long long)total_units * cuts;
   const uint32_t want = (uint32_t)(p.world_size * p.splits);
   uint32_t* counters = peer_ptr<uint32_t>(p.peer_base[p.rank], p.off_counters);
   const __nv_bfloat16* stage = peer_ptr<const __nv_bfloat16>(p.peer_base[p.rank], p.off_stage);
@@ -461,9 +469,11 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
     if (lane == 0) li = atomicAdd(next_unit, 1);
     li = __shfl_sync(0xffffffffu, li, 0);
     const long long j = (long long)first + (long long)li * G;
-    if (j >= total_units) break;
-    const int part = (int)(j % parts);
-    const int rest = (int)(j / parts);
+    if (j >= total_work) break;
+    const int cut = (int)(j % cuts);
+    const int unit = (int)(j / cuts);
+    const int part = unit % parts;
+    const int rest = unit / parts;
     const int mi = rest % n_mb;
     const int nb = rest / n_mb;
     const int mb = all_staged ? mb_lo + mi : ((mi == 0 && lo_staged) ? mb_lo : mb_hi);
@@ -498,15 +508,21 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
       const int c0 = nb * BN;
       const int c1 = min(c0 + BN, p.N);
       const int vec_per_row = (c1 - c0) >> 3;
-      if (p.splits > 1) {
-        reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row,
-                            (r1 - r0) * vec_per_row, lane);
-      } else {
-        reduce_block(p, stage, r0, row_lo, c0, vec_per_row, (r1 - r0) * vec_per_row, lane);
+      const int items = (r1 - r0) * vec_per_row;
+      const int lo = cut * cut_items;
+      const int hi = min(items, lo + cut_items);
+      if (lo < hi) {
+        if (p.splits > 1) reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row, lo, hi, lane);
+        else reduce_block(p, stage, r0, row_lo, c0, vec_per_row, lo, hi, lane);
       }
     }
     __syncwarp();
-    if (lane < ctrs_per_part) ctr[lane] = 0;  // this parity's counters are next used two calls from now
+    if (lane < ctrs_per_part) {
+      // Every cut of the unit adds one to its counters when it is done; the one that sees all the
+      // others' marks zeroes them (this parity's counters are next used two calls from now).
+      const uint32_t old = atomicAdd(ctr + lane, 1u);
+      if (old == want + (uint32_t)cuts - 1u) ctr[lane] = 0;
+    }
   }
 }
 

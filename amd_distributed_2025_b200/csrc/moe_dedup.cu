@@ -32,6 +32,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "moe.h"
 #include "moe_common.cuh"
@@ -594,15 +595,19 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
           }
         }
       } else if (piece == 0) {
-        for (int h = lane; h < p.hidden; h += 32) {
+        // the trip count is the same for every lane: the shuffles below need the whole warp
+        for (int h0 = 0; h0 < p.hidden; h0 += 32) {
+          const int h = h0 + lane;
           float acc = 0.f;
           for (int c = 0; c < cnt; ++c) {
             const int r = __shfl_sync(0xffffffffu, crow, c);
             const float wc = __shfl_sync(0xffffffffu, cw, c);
-            acc = fmaf(to_f32(__ldcg(reinterpret_cast<const T*>(ey + (size_t)r * row_bytes) + h)), wc, acc);
+            if (h < p.hidden) acc = fmaf(to_f32(__ldcg(reinterpret_cast<const T*>(ey + (size_t)r * row_bytes) + h)), wc, acc);
           }
-          if (p.partial_fp32 && !direct_out) reinterpret_cast<float*>(dst_row)[h] = acc;
-          else reinterpret_cast<T*>(dst_row)[h] = from_f32<T>(acc);
+          if (h < p.hidden) {
+            if (p.partial_fp32 && !direct_out) reinterpret_cast<float*>(dst_row)[h] = acc;
+            else reinterpret_cast<T*>(dst_row)[h] = from_f32<T>(acc);
+          }
         }
       }
     }
@@ -720,6 +725,19 @@ namespace {
 
 bool dedup_small(int num_entries, int num_experts) { return num_entries <= 4096 && num_experts <= 2048; }
 
+// Kernels without a grid barrier wait only on flags that the LAST CTA of a grid raises, so all
+// they need is that every CTA gets an SM eventually: the grid is sized to fit the device at
+// once (occupancy x SMs) and launched the ordinary way, which costs several microseconds less
+// per launch than a cooperative launch.  B200_COOP_LAUNCH=1 makes the runtime enforce the
+// co-residency (e.g. when other work shares the device).  Waits are bounded either way.
+bool force_cooperative() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200_COOP_LAUNCH");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return on;
+}
+
 size_t dispatch_smem(bool small, int num_entries, int num_experts) {
   if (small) return ((size_t)((num_entries + 31) & ~31) + 2 * (size_t)num_experts) * sizeof(int32_t);
   return (size_t)(kWarps + 2) * num_experts * sizeof(int32_t);
@@ -732,9 +750,13 @@ cudaError_t launch_dispatch_typed(const MoeDedupDispatchParams& p, int grid, siz
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
+  if (SMALL && !force_cooperative()) {
+    kernel<<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+  }
   MoeDedupDispatchParams params = p;
   void* args[] = {&params};
-  // Cooperative launch: CTAs wait on one another (grid barrier, last-CTA flags), so they must be co-resident.
+  // Cooperative launch: CTAs meet on a grid barrier, so they must be co-resident.
   return cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), args, smem, stream);
 }
 
@@ -814,6 +836,15 @@ cudaError_t launch_moe_dedup_dispatch(const MoeDedupDispatchParams& p, int grid,
 
 cudaError_t launch_moe_dedup_combine(const MoeDedupCombineParams& p, int grid, cudaStream_t stream) {
   if (p.k < 1 || p.k > 32 || p.world_size > kMaxWorldSize) return cudaErrorInvalidValue;
+  if (!force_cooperative()) {
+    switch (p.dtype) {
+      case 0: moe_dedup_combine_kernel<__half><<<grid, kThreads, 0, stream>>>(p); break;
+      case 1: moe_dedup_combine_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p); break;
+      case 2: moe_dedup_combine_kernel<float><<<grid, kThreads, 0, stream>>>(p); break;
+      default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+  }
   MoeDedupCombineParams params = p;
   void* args[] = {&params};
   const void* kernel = nullptr;

@@ -67,6 +67,8 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=128)
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--few-launches", action="store_true",
+                    help="for a run under a profiler: one warm-up call, --iters timed calls, no host-time loop")
     ap.add_argument("--fuse-own", choices=["auto", "on", "off"], default="auto",
                     help="gemm_rs on several ranks: finish own tiles in their epilogue, or in a pass after the GEMM tiles")
     args = ap.parse_args(argv)
@@ -90,7 +92,8 @@ def main(argv=None) -> int:
         times = timing.time_cuda(lambda: op(a, w, bias), warmup=3 if ws > 1 else 1, iters=args.iters,
                                  barrier=dist.barrier if ws > 1 else None)
         op.check()
-        out["host_us"] = _host_time_us(lambda: gemm_rs.custom_kernel((a, w, bias)), ws)
+        if not args.few_launches:
+            out["host_us"] = _host_time_us(lambda: gemm_rs.custom_kernel((a, w, bias)), ws)
         if args.trace:
             op.trace.zero_()
         y = op(a, w, bias)
@@ -122,7 +125,8 @@ def main(argv=None) -> int:
         fn = lambda: moe_all2all.custom_kernel((cfg, data, rank, ws), mode=args.mode)  # noqa: E731
         times = timing.time_cuda(fn, warmup=3 if ws > 1 else 1, iters=args.iters, barrier=dist.barrier if ws > 1 else None)
         layer = moe_all2all.get_layer(cfg, rank, ws, mode=args.mode)
-        out["host_us"] = _host_time_us(fn, ws)
+        if not args.few_launches:
+            out["host_us"] = _host_time_us(fn, ws)
         if args.trace and layer.engine is not None:
             layer.enable_trace(True)
         y = fn()

@@ -76,29 +76,42 @@ class GemmRS:
             poison_on_timeout=True,
         )
         self.monitor = monitor  # optional parallel.health.HealthMonitor: peers are checked before every launch
-        self.checked = checked()
-        self._plans: Dict[tuple, dict] = {}
+        self.engine = self.ext.GemmRsEngine(
+            self.ws.heap, [self.ws.offset("stage0"), self.ws.offset("stage1")],
+            [self.ws.offset("counters0"), self.ws.offset("counters1")], self.stage_bytes, self.counter_bytes,
+            self.ws.wait_limit_ns,
+        )
+        self.engine.checked = checked()
         self._fits = set()  # problem sizes already known to fit this workspace
-        self.max_ctas = 0  # 0 = one CTA per SM
-        self.block_n = 0  # 0 = tile width chosen from the shape (64 / 128 / 192 / 256)
-        self.cta_pair = -1  # -1 = chosen from the shape; 0 = single CTAs; 1 = CTA pairs (256-row tiles)
-        self.splits = 0  # 0 = chosen from the shape; else K slices per tile
         self.trace: Optional[torch.Tensor] = None  # int64 [160, 8]: per-CTA globaltimer stamps when set
-        self.debug = 0  # measurement aids that make results wrong: 1 = stage locally, 2 = do not stage
-        # True: a rank's own tiles add the peers' rows in their epilogue; False: own tiles are staged like
-        # the others and all CTAs reduce after the GEMM tiles; None: fused up to 4 ranks (few rows to
-        # fetch per tile), separate pass beyond
-        self.fuse_own: Optional[bool] = None
-        self.tma_store = True  # staged tiles leave through TMA stores where the shape allows
-        self.force_staged = False  # stage and reduce even on one rank (tests the staged path on one GPU)
+
+    # Knobs of the native engine (0 / -1 / None = chosen from the shape): ``max_ctas`` (0 = one CTA per
+    # SM), ``block_n`` (64 / 128 / 192 / 256), ``cta_pair`` (0 = single CTAs, 1 = CTA pairs with
+    # 256-row tiles), ``splits`` (K slices per tile), ``debug`` (measurement aids that make results
+    # wrong: 1 = stage locally, 2 = do not stage), ``fuse_own`` (True: a rank's own tiles add the
+    # peers' rows in their epilogue; False: they are staged like the others and reduced by the reducer
+    # warps; None: fused up to 4 ranks), ``tma_store`` (staged tiles leave through TMA stores where
+    # the shape allows), ``force_staged`` (stage and reduce even on one rank).
+    max_ctas = property(lambda self: self.engine.max_ctas, lambda self, v: setattr(self.engine, "max_ctas", int(v)))
+    block_n = property(lambda self: self.engine.block_n, lambda self, v: setattr(self.engine, "block_n", int(v)))
+    cta_pair = property(lambda self: self.engine.cta_pair, lambda self, v: setattr(self.engine, "cta_pair", int(v)))
+    splits = property(lambda self: self.engine.splits, lambda self, v: setattr(self.engine, "splits", int(v)))
+    debug = property(lambda self: self.engine.debug, lambda self, v: setattr(self.engine, "debug", int(v)))
+    tma_store = property(lambda self: self.engine.tma_store, lambda self, v: setattr(self.engine, "tma_store", bool(v)))
+    force_staged = property(lambda self: self.engine.force_staged,
+                            lambda self, v: setattr(self.engine, "force_staged", bool(v)))
+
+    @property
+    def fuse_own(self) -> Optional[bool]:
+        v = self.engine.fuse_own
+        return None if v < 0 else bool(v)
+
+    @fuse_own.setter
+    def fuse_own(self, v: Optional[bool]) -> None:
+        self.engine.fuse_own = -1 if v is None else int(bool(v))
 
     def plan(self, m: int, n: int, k: int) -> dict:
-        key = (m, n, k, self.block_n, self.cta_pair, self.splits)
-        plan = self._plans.get(key)
-        if plan is None:
-            plan = self.ext.gemm_rs_plan(m, n, k, self.world_size, self.block_n, self.cta_pair, self.splits)
-            self._plans[key] = plan
-        return plan
+        return self.engine.plan(m, n, k)
 
     def fits(self, plan: dict) -> bool:
         return plan["stage_bytes"] <= self.stage_bytes and plan["counter_bytes"] <= self.counter_bytes
@@ -111,47 +124,23 @@ class GemmRS:
         bias_mode: str = "per_rank",
         out: Optional[torch.Tensor] = None,
     ) -> torch.Tensor:
-        m, n, k = a.shape[0], w.shape[0], a.shape[1]
-        plan = self.plan(m, n, k)
-        if not self.fits(plan):
-            raise ValueError(f"problem {m}x{n}x{k} needs {plan['stage_bytes']} staging bytes, workspace has {self.stage_bytes}")
-        if bias_mode not in ("per_rank", "once"):
+        # "per_rank": every rank adds the bias to its rounded partial before the reduction
+        # (the reference's order of operations); "once": the owner adds it after the sum.
+        if bias_mode != "per_rank" and bias_mode != "once":
             raise ValueError("bias_mode must be 'per_rank' or 'once'")
-        self.ws.check()
+        if self.ws.poisoned is not None:
+            self.ws.check()
         if self.monitor is not None:
             self.monitor.beat()
             self.monitor.assert_all_alive()
         if out is None:
-            out = torch.empty((m // self.world_size, n), dtype=torch.bfloat16, device=a.device)
-        epoch = self.ws.next_epoch("gemm_rs")
-        parity = epoch & 1
-        # "per_rank": every rank adds the bias to its rounded partial before the reduction
-        # (the reference's order of operations); "once": the owner adds it after the sum.
-        at_source = bias_mode == "per_rank"
-        self.ext.gemm_rs(
-            self.ws.heap,
-            a.contiguous(),
-            w.contiguous(),
-            bias,
-            out,
-            1.0,
-            at_source,
-            self.ws.offset(f"stage{parity}"),
-            self.ws.offset(f"counters{parity}"),
-            epoch,
-            self.ws.wait_limit_ns,
-            self.max_ctas,
-            plan["block_n"],
-            plan["cta_pair"],
-            plan["splits"],
-            self.trace,
-            self.debug,
-            (self.world_size <= 4) if self.fuse_own is None else bool(self.fuse_own),
-            self.tma_store,
-            self.force_staged,
-            self.checked,
-            self.stage_bytes,
-        )
+            out = torch.empty((a.shape[0] // self.world_size, w.shape[0]), dtype=torch.bfloat16, device=a.device)
+        if not a.is_contiguous():
+            a = a.contiguous()
+        if not w.is_contiguous():
+            w = w.contiguous()
+        if self.engine.run(a, w, bias, out, bias_mode == "per_rank", 1.0):
+            self.ws.check()  # an earlier kernel recorded a failure: raise it (and poison if need be)
         return out
 
     def enable_trace(self, on: bool = True) -> None:
@@ -159,6 +148,7 @@ class GemmRS:
         kernel start, pipeline ready, GEMM tiles done, exit, first own tile reached, its
         peers' rows arrived, last own tile stored."""
         self.trace = torch.zeros((160, 8), dtype=torch.int64, device=self.device) if on else None
+        self.engine.set_trace(self.trace)
 
     def check(self, sync: bool = True) -> None:
         self.ws.check(sync)
@@ -168,6 +158,7 @@ class GemmRS:
         """Collective: make the workspace usable again after an expired wait (both parities of
         the arrival counters zeroed on every rank, call numbers restarted)."""
         self.ws.recover(("counters0", "counters1"))
+        self.engine.restart_epochs()
 
     def close(self, collective: bool = False) -> None:
         self.ws.close(collective)
@@ -181,16 +172,18 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
 
     The workspace is sized for ``splits_hint`` K slices of an ``m x n`` output when the
     problem is small (so forcing more slices in experiments still fits), else for the plan.
+    Growing frees and re-creates the workspace (a device synchronisation, a host barrier and
+    new peer mappings), so a serving loop should make its first call with the largest shape.
     """
+    key = (id(group), torch.cuda.current_device())
+    op = _OPS.get(key)
+    if op is not None and (m, n, k) in op._fits:
+        return op
     from ..ops import _ext
 
     ext = _ext.load()
     initialized = dist.is_available() and dist.is_initialized()
     ws = dist.get_world_size(group) if initialized else 1
-    key = (ws, id(group), torch.cuda.current_device())
-    op = _OPS.get(key)
-    if op is not None and (m, n, k) in op._fits:
-        return op
     plan = ext.gemm_rs_plan(m, n, max(k, 64), ws, 0, -1, 0)
     need_stage = plan["stage_bytes"]
     if m * n * 2 * splits_hint <= (256 << 20):
@@ -206,6 +199,7 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
         op.close(collective=True)
         need_stage, need_counters = max(need_stage, op.stage_bytes), max(need_counters, op.counter_bytes)
     op = GemmRS(need_stage, need_counters, group=group)
+    op._fits.add((m, n, k))
     _OPS[key] = op
     return op
 

@@ -185,7 +185,8 @@ class MoEAllToAll:
         idx = indices.to(torch.int32).contiguous()
         self._num_tokens = x.shape[0]
         if self.engine is not None:
-            self.engine.dispatch(x, idx)
+            if self.engine.dispatch(x, idx):
+                self.ws.check()
             return self.expert_num_tokens, self.expert_x, self.expert_meta
         self.ext.moe_dispatch(
             self.ws.heap,
@@ -243,7 +244,8 @@ class MoEAllToAll:
             target = out_tokens
             if accumulate or not out_tokens.is_contiguous() or out_tokens.dtype != self.cfg.out_dtype:
                 target = torch.empty((max(n, 1), self.cfg.hidden_dim), dtype=self.cfg.out_dtype, device=out_tokens.device)
-            self.engine.combine(target, weights.to(torch.float32).contiguous(), expert_y.contiguous())
+            if self.engine.combine(target, weights.to(torch.float32).contiguous(), expert_y.contiguous()):
+                self.ws.check()
             if target is not out_tokens:
                 if accumulate:
                     out_tokens[:n] += target[:n].to(out_tokens.dtype)
@@ -278,21 +280,27 @@ class MoEAllToAll:
     # -- the task pipeline in one native call -------------------------------------------
     def forward(self, dp_x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, scale: float) -> torch.Tensor:
         """dispatch -> ``expert_y = expert_x * scale`` -> combine, launched back to back from
-        one native call (same kernels and protocol as the three separate methods)."""
+        one native call.  In "dedup" mode the scale is applied while the landed rows are
+        replicated into the expert buffers (two launches); in "direct" mode it is the three
+        kernels of the separate methods."""
         cfg = self.cfg
         if dp_x.shape[0] > cfg.max_num_tokens or dp_x.shape[1] != cfg.hidden_dim or dp_x.dtype != cfg.in_dtype:
             raise ValueError("dp_x does not match the configuration")
         if indices.shape[1] != cfg.experts_per_token:
             raise ValueError("indices do not match the configuration")
-        self._guard()
+        if self.monitor is not None:
+            self.monitor.beat()
+            self.monitor.assert_all_alive()
         x = dp_x if dp_x.is_contiguous() else dp_x.contiguous()
         idx = indices if (indices.dtype == torch.int32 and indices.is_contiguous()) else indices.to(torch.int32).contiguous()
         w = weights if (weights.dtype == torch.float32 and weights.is_contiguous()) else weights.to(torch.float32).contiguous()
         self._num_tokens = x.shape[0]
         out = torch.empty((x.shape[0], cfg.hidden_dim), dtype=cfg.out_dtype, device=x.device)
         if self.engine is not None:
-            self.engine.forward(x, idx, w, out, float(scale))
+            if self.engine.forward(x, idx, w, out, float(scale)):
+                self.ws.check()  # an earlier kernel recorded a failure: raise it
             return out
+        self.ws.check()
         self.ext.moe_forward(
             self.ws.heap, x, idx, w, out, cfg.num_experts, self.max_recv,
             self._off_counts, self._off_expert_x, self._off_expert_meta, self._off_expert_y,
@@ -321,29 +329,24 @@ def get_layer(cfg: MoEConfig, rank: int, world_size: int, group=None, mode: Opti
     """Workspace creation is collective and costs milliseconds, so layers are cached per
     configuration; the reference rebuilds its helper object on every call
     (all2all/hipv8.py:379) because it owns no persistent state."""
-    key = (
-        cfg.num_experts,
-        cfg.experts_per_token,
-        cfg.hidden_dim,
-        cfg.max_num_tokens,
-        cfg.in_dtype,
-        cfg.out_dtype,
-        rank,
-        world_size,
-        id(group),
-        torch.cuda.current_device(),
-        mode or default_mode(),
-    )
+    key = (cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens, cfg.in_dtype, cfg.out_dtype,
+           rank, world_size, id(group), mode)
     layer = _LAYERS.get(key)
     if layer is None:
-        layer = MoEAllToAll(cfg, rank, world_size, group, mode=mode)
-        _LAYERS[key] = layer
+        resolved = mode or default_mode()
+        full = key[:-1] + (resolved, torch.cuda.current_device())
+        layer = _LAYERS.get(full)
+        if layer is None:
+            layer = MoEAllToAll(cfg, rank, world_size, group, mode=resolved)
+            _LAYERS[full] = layer
+        if torch.cuda.device_count() == 1 or world_size > 1:
+            _LAYERS[key] = layer  # short key: one device per process, so the device need not be part of it
     return layer
 
 
 def release_layers() -> None:
     """Free every cached workspace (collective: all ranks must call it while idle)."""
-    for layer in _LAYERS.values():
+    for layer in {id(v): v for v in _LAYERS.values()}.values():
         layer.close(collective=True)
     _LAYERS.clear()
 

@@ -71,7 +71,9 @@ def verify_output(item, y: torch.Tensor, rank: int, ws: int, device: torch.devic
     error against the un-rounded fp32 sum over all ranks' operands (the task tolerance is vacuous
     or noise-dominated for these operand distributions, see oracle.outlier_fraction)."""
     if item["kind"] == "moe":
-        want = oracle.moe_expected_output(item["cfg"], item["data"], ws, emulate_reference_rounding=True)
+        # against the exact weighted sum (fp64, one rounding): with bf16 the reference's own
+        # per-add rounding strays further from it than the task tolerance allows
+        want = oracle.moe_expected_output(item["cfg"], item["data"], ws)
         ok, _ = oracle.check_moe_output(y, want)
         return bool(ok)
     c = item["spec"]
