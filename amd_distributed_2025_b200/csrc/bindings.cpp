@@ -283,7 +283,8 @@ class MoeDedupEngine {
     p.max_tokens = (int32_t)max_tokens_;
     p.dtype = dtype_code_;
     p.row_bytes = (uint32_t)(H_ * elem_);
-    p.pieces = pieces_for((int)T, max_blocks);
+    p.pieces = pieces_for((int)T, max_blocks, 1);
+    p.rep_pieces = pieces_for((int)T, max_blocks, 12);
     p.fuse_scale = fuse_scale ? 1 : 0;
     p.scale = (float)scale;
     p.epoch = (uint64_t)(++dispatch_epoch_);
@@ -340,7 +341,7 @@ class MoeDedupEngine {
     p.dtype = dtype_code_;
     p.partial_fp32 = partial_fp32_ ? 1 : 0;
     p.weights_sent = weights_sent_ ? 1 : 0;
-    p.pieces = pieces_for((int)T, combine_blocks_);
+    p.pieces = pieces_for((int)T, combine_blocks_, 4);
     p.epoch = (uint64_t)(++combine_epoch_);
     p.dispatch_epoch = (uint64_t)dispatch_epoch_;
     p.timeout_ns = (uint64_t)timeout_ns_;
@@ -369,14 +370,17 @@ class MoeDedupEngine {
     keep_.push_back(*t);
     return reinterpret_cast<uint64_t*>(t->data_ptr<int64_t>());
   }
-  // A row is split over several warps when there are fewer tokens than warps (decode).
-  int pieces_for(int tokens, int blocks) const {
+  // A row is split over several warps so that there are about `per_warp` (row, piece) items for
+  // every warp of the grid: one when a row's latency matters (decode), a dozen when the point is
+  // that all warps get nearly equal shares.  Power of two, at most 8, at least 1 KiB per piece.
+  int pieces_for(int tokens, int blocks, int per_warp) const {
     const int64_t row_bytes = H_ * elem_;
     if (row_bytes % 16 != 0) return 1;
     const int nv = (int)(row_bytes / 16);
-    int pcs = (blocks * 8) / std::max(tokens * heap_->world_size(), 1);
-    pcs = std::min(pcs, std::max(nv / 64, 1));  // at least 1 KiB per piece
-    return std::max(1, std::min(pcs, 8));
+    const int64_t want = ((int64_t)per_warp * blocks * 8) / std::max<int64_t>((int64_t)tokens * heap_->world_size(), 1);
+    int pcs = 1;
+    while (pcs < 8 && pcs * 2 <= want && nv / (pcs * 2) >= 64) pcs *= 2;
+    return pcs;
   }
 
   std::shared_ptr<SymmHeap> heap_;

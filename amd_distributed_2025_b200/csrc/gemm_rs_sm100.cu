@@ -104,7 +104,9 @@ struct KernelParams {
   uint64_t epoch, timeout_ns;
   StatusBlock* status;
   uint64_t* trace;  // optional [gridDim.x][8] globaltimer stamps: 0 start, 1 pipeline ready, 2 GEMM tiles done,
-                    // 3 exit, 4 first own tile reached, 5 its peers' rows arrived, 6 last own tile stored
+                    // 3 exit; with own tiles finished in the epilogue: 4 first own tile reached, 5 its peers'
+                    // rows arrived, 6 last own tile stored; else, for the first epilogue warp once it has
+                    // joined the reducers: 5 its first unit complete, 6 its last unit reduced
   int debug;        // measurement aids (results are wrong when set): 1 = stage into this GPU's own memory
                     // instead of the owner's, 2 = skip the staging stores
   int fuse_own;     // 1: a rank finishes its own tiles in their epilogue (adds the peers' rows there);
@@ -434,7 +436,8 @@ __device__ __forceinline__ void reduce_block_sliced(const KernelParams& p, const
 // boundary (always the case when a rank owns fewer than 128 rows) and all tiles of a K-sliced
 // problem were staged by every (virtual) rank, this one included.
 template <int BN>
-__device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* next_unit, volatile int* abort, int lane) {
+__device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* next_unit, volatile int* abort, int lane,
+                                                    bool stamps) {
   const int G = gridDim.x;
   const int R = p.rows_per_rank;
   const int row_lo = p.rank * R;
@@ -502,6 +505,7 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
     }
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
+    if (stamps && lane == 0) trace_stamp_any(p, 5, true);  // first unit of this warp is complete
     const int r0 = max(mb * BM + part * rows_per_part, row_lo);
     const int r1 = min(min(mb * BM + (part + 1) * rows_per_part, row_lo + R), p.M);
     if (r1 > r0) {
@@ -523,6 +527,7 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
       const uint32_t old = atomicAdd(ctr + lane, 1u);
       if (old == want + (uint32_t)cuts - 1u) ctr[lane] = 0;
     }
+    if (stamps && lane == 0) trace_stamp_any(p, 6, false);  // latest unit this warp has finished
   }
 }
 
@@ -949,7 +954,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   } else {
     // ================================ reducers ==========================================
-    if (!p.direct) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane);
+    if (!p.direct) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane, false);
   }
 
   // ================================ end of the GEMM phase ================================
@@ -964,7 +969,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     asm volatile("bar.sync 1, %0;" ::"n"(kMainThreads) : "memory");
     trace_stamp(p, 2);
     // ... and help with what is left of the reduction
-    if (!p.direct && !abort_flag) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane);
+    if (!p.direct && !abort_flag) reduce_staged_units<BN>(p, &next_unit_shared, &abort_flag, lane, warp == 2 && !p.fuse_own);
   }
 
   // ================================ teardown =============================================

@@ -104,7 +104,8 @@ struct MoeDedupDispatchParams {
   int32_t num_tokens, k, num_experts, num_local_experts, world_size, rank, max_recv, max_tokens;
   int32_t dtype;             // 0 = fp16, 1 = bf16, 2 = fp32
   uint32_t row_bytes;
-  int32_t pieces;            // a row is moved by this many warps (small problems)
+  int32_t pieces;            // a row is landed by this many warps (small problems)
+  int32_t rep_pieces;        // a landed row is replicated by this many warps (evens out the warps' shares)
   int32_t fuse_scale;        // 1: the replication pass also writes expert_y = expert_x * scale
   float scale;
   uint64_t epoch, timeout_ns;

@@ -160,12 +160,14 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   const int G = gridDim.x;
   const int W = G * kWarps;
   const int gw = blockIdx.x * kWarps + warp;
-  const int P = SMALL ? p.pieces : 1;
+  const int P = SMALL ? p.pieces : 1;   // pieces of a row in the landing pass
+  const int PR = p.rep_pieces;           // ... and in the replication pass
   const uint64_t my_base = p.peer_base[p.rank];
   const uint32_t epoch32 = (uint32_t)p.epoch;
   const bool vec16 = (p.row_bytes & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0;
   const int nv = (int)(p.row_bytes >> 4);
   const int pv = (nv + P - 1) / P;  // vectors per piece
+  const int pvr = (nv + PR - 1) / PR;
   const int hidden = (int)(p.row_bytes / sizeof(T));
   const uint8_t* xbytes = reinterpret_cast<const uint8_t*>(p.x);
   uint32_t bar_target = 0;
@@ -247,13 +249,22 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     // base[e] = entries of this rank in lower CTAs; tot[e] = all of them (publishing CTAs only).
     // One coalesced pass over the histogram rows with shared-memory adds keeps every thread busy.
     const int rows = ((int)blockIdx.x < p.world_size) ? G : (int)blockIdx.x;
-    for (int idx = tid; idx < rows * E; idx += kThreads) {
-      const int g = idx / E;
-      const int e = idx - g * E;
-      const int c = __ldcg(p.blk_hist + idx);
-      if (c != 0) {
-        if (g < (int)blockIdx.x) atomicAdd(&s_base[e], c);
-        atomicAdd(&s_tot[e], c);
+    const int lim = rows * E;
+    for (int base = tid; base < lim; base += kThreads * 8) {
+      int c[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // eight loads in flight per thread
+        const int idx = base + u * kThreads;
+        c[u] = idx < lim ? __ldcg(p.blk_hist + idx) : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c[u] == 0) continue;
+        const int idx = base + u * kThreads;
+        const int g = idx / E;
+        const int e = idx - g * E;
+        if (g < (int)blockIdx.x) atomicAdd(&s_base[e], c[u]);
+        atomicAdd(&s_tot[e], c[u]);
       }
     }
     __syncthreads();
@@ -417,9 +428,9 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     alive = cta_wait_one(my_base, FLAG_MOE_DATA, s, p.epoch, p.timeout_ns, p.status, PHASE_MOE_DATA);
     if (!alive) break;
     if (j == p.world_size - 1) stamp(p.trace, 5);
-    for (int item = gw; item < p.max_tokens * P; item += W) {
-      const int t = item / P;
-      const int piece = item - t * P;
+    for (int item = gw; item < p.max_tokens * PR; item += W) {
+      const int t = item / PR;
+      const int piece = item - t * PR;
       const uint64_t rec = (uint64_t)s * p.max_tokens + t;
       if (__ldcg(tok_mark + rec) != epoch32) continue;
       int row = -1;
@@ -442,7 +453,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
         return d;
       };
       if (vec16) {
-        const int v_lo = piece * pv, v_hi = min(nv, (piece + 1) * pv);
+        const int v_lo = piece * pvr, v_hi = min(nv, (piece + 1) * pvr);
         if (p.fuse_scale) warp_fanout<T, true>(reinterpret_cast<const int4*>(src), v_lo, v_hi, lane, k, p.scale, dst_of);
         else warp_fanout<T, false>(reinterpret_cast<const int4*>(src), v_lo, v_hi, lane, k, 0.f, dst_of);
       } else if (piece == 0) {
