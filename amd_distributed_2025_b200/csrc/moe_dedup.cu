@@ -37,6 +37,7 @@
 #include "moe.h"
 #include "moe_common.cuh"
 #include "signal.cuh"
+#include "sm100_ptx.cuh"
 
 namespace b200 {
 
@@ -134,6 +135,87 @@ __device__ __forceinline__ bool last_cta_arrives(uint32_t* counter) {
   }
   __syncthreads();
   return is_last != 0;
+}
+
+// ---- weighted sum of rows through shared memory ------------------------------------------------
+// Register loads keep at most a few KiB per warp in flight, which leaves a reduction over
+// scattered 8-16 KiB rows latency-bound at under half of the memory bandwidth.  Here every row's
+// run of bytes is fetched by ONE bulk copy (cp.async.bulk, completion counted on the warp's
+// mbarrier), so a warp has its whole stage in flight and sixteen warps keep ~190 KiB per SM
+// moving; the sum is then formed from shared memory.
+constexpr int kStageBytes = 12288;  // per warp
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns, StatusBlock* st,
+                                                  uint32_t phase) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0 && global_timer_ns() - t0 > limit_ns) {
+      record_status(st, STATUS_TIMEOUT, phase, -1, (int)blockIdx.x, 0, parity);
+      return false;
+    }
+  }
+  return true;
+}
+
+// One warp: dst[v] = sum over c < cnt (ascending) of w_c * row_c[v] for the 16-byte vectors
+// v in [v_lo, v_hi) of rows of T.  Lane c holds row_c (a local pointer, 16-byte aligned) and w_c.
+// `stage` / `stage_u32` is this warp's shared-memory stage, `bar` its mbarrier (count 1), `parity`
+// the phase to wait for next.  With OUT_FP32 the sums are stored un-rounded (4 bytes per element).
+// Returns false if a copy did not complete within the limit (recorded).
+template <typename T, bool OUT_FP32>
+__device__ __forceinline__ bool warp_weighted_sum_bulk(const uint8_t* row, float w, int cnt, int v_lo, int v_hi,
+                                                       uint8_t* dst_row, const uint8_t* stage, uint32_t stage_u32,
+                                                       uint32_t bar, uint32_t& parity, int lane, uint64_t limit_ns,
+                                                       StatusBlock* st) {
+  constexpr int N = Vec16<T>::N;
+  constexpr int CU = 4;
+  int cv = kStageBytes / 16 / cnt;  // vectors per row that fit the stage together with the other rows
+  cv = cv >= 32 ? (cv & ~31) : cv;
+  for (int vc = v_lo; vc < v_hi; vc += cv) {
+    const int nvc = min(cv, v_hi - vc);
+    const uint32_t cb = (uint32_t)nvc * 16u;
+    if (lane == 0) ptx::mbar_arrive_expect_tx(bar, cb * (uint32_t)cnt);
+    __syncwarp();
+    if (lane < cnt) ptx::bulk_load(stage_u32 + (uint32_t)lane * cb, row + (size_t)vc * 16, cb, bar);
+    if (!mbar_wait_bounded(bar, parity, limit_ns, st, PHASE_MOE_RETURN)) return false;
+    parity ^= 1u;
+    for (int v0 = 0; v0 < nvc; v0 += 32 * CU) {
+      float acc[CU][N];
+#pragma unroll
+      for (int u = 0; u < CU; ++u)
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[u][e] = 0.f;
+      for (int c = 0; c < cnt; ++c) {
+        const float wc = __shfl_sync(0xffffffffu, w, c);
+        const int4* srow = reinterpret_cast<const int4*>(stage + (size_t)c * cb);
+#pragma unroll
+        for (int u = 0; u < CU; ++u) {
+          const int idx = v0 + lane + 32 * u;
+          if (idx < nvc) fma_vec<T>(acc[u], srow[idx], wc);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < CU; ++u) {
+        const int idx = v0 + lane + 32 * u;
+        if (idx >= nvc) continue;
+        const size_t gv = (size_t)vc + idx;
+        if (OUT_FP32) {
+          float4* d4 = reinterpret_cast<float4*>(dst_row) + gv * (N / 4);
+#pragma unroll
+          for (int q = 0; q < N / 4; ++q)
+            d4[q] = make_float4(acc[u][4 * q], acc[u][4 * q + 1], acc[u][4 * q + 2], acc[u][4 * q + 3]);
+        } else {
+          reinterpret_cast<int4*>(dst_row)[gv] = pack_vec<T>(acc[u]);
+        }
+      }
+    }
+    // every lane is done reading the stage before the next copies may overwrite it
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+  }
+  return true;
 }
 
 }  // namespace
@@ -492,6 +574,20 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
   stamp(p.trace, 0);
   bool alive = true;
 
+  // this warp's stage and mbarrier for the bulk-copy reductions
+  extern __shared__ __align__(128) uint8_t smem_stage[];
+  __shared__ uint64_t stage_bars[kWarps];
+  const uint8_t* stage = smem_stage + (size_t)warp * kStageBytes;
+  const uint32_t stage_u32 = ptx::smem_u32(stage);
+  const uint32_t bar = ptx::smem_u32(&stage_bars[warp]);
+  uint32_t parity = 0;
+  if (tid == 0) {
+    for (int wi = 0; wi < kWarps; ++wi) ptx::mbar_init(ptx::smem_u32(&stage_bars[wi]), 1);
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  __syncthreads();
+
   // ---- phase 0: deliver the routing weights to the owners (when dispatch did not) ----------
   if (!p.weights_sent) {
     for (int t = gw; t < p.num_tokens; t += W) {
@@ -528,7 +624,8 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
   const uint8_t* ey = reinterpret_cast<const uint8_t*>(p.expert_y);
   const int total_rows = p.num_local_experts * p.max_recv;
   const bool direct_out = p.world_size == 1;  // the only owner is the source: write the result itself
-  for (int j = 0; j < p.world_size && alive; ++j) {
+  bool warp_ok = true;
+  for (int j = 0; j < p.world_size && alive && warp_ok; ++j) {
     int s = p.rank + 1 + j;  // remote sources first, rotated so that the ranks do not all push to the same one
     if (s >= p.world_size) s -= p.world_size;
     for (int item = gw; item < p.max_tokens * P; item += W) {
@@ -559,51 +656,18 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
                                    ((uint64_t)p.rank * p.max_tokens + t) * ret_row_bytes;
       if (vec16) {
         const int v_lo = piece * pv, v_hi = min(nv, (piece + 1) * pv);
-        for (int v0 = v_lo; v0 < v_hi; v0 += 32 * CU) {
-          float acc[CU][N];
-#pragma unroll
-          for (int u = 0; u < CU; ++u)
-#pragma unroll
-            for (int e = 0; e < N; ++e) acc[u][e] = 0.f;
-          for (int c = 0; c < cnt; c += 2) {
-            const int r0 = __shfl_sync(0xffffffffu, crow, c);
-            const float w0 = __shfl_sync(0xffffffffu, cw, c);
-            const bool two = c + 1 < cnt;
-            const int r1 = __shfl_sync(0xffffffffu, crow, two ? c + 1 : c);
-            const float w1 = two ? __shfl_sync(0xffffffffu, cw, c + 1) : 0.f;
-            const int4* s0 = reinterpret_cast<const int4*>(ey + (size_t)r0 * row_bytes);
-            const int4* s1 = reinterpret_cast<const int4*>(ey + (size_t)r1 * row_bytes);
-            int4 a[CU], b[CU];
-#pragma unroll
-            for (int u = 0; u < CU; ++u) {
-              const int idx = v0 + lane + 32 * u;
-              if (idx < v_hi) {
-                a[u] = __ldcg(s0 + idx);
-                b[u] = two ? __ldcg(s1 + idx) : make_int4(0, 0, 0, 0);
-              } else {
-                a[u] = make_int4(0, 0, 0, 0);
-                b[u] = make_int4(0, 0, 0, 0);
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < CU; ++u) {
-              fma_vec<T>(acc[u], a[u], w0);
-              fma_vec<T>(acc[u], b[u], w1);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < CU; ++u) {
-            const int idx = v0 + lane + 32 * u;
-            if (idx >= v_hi) continue;
-            if (p.partial_fp32 && !direct_out) {
-              float4* d4 = reinterpret_cast<float4*>(dst_row) + (size_t)idx * (N / 4);
-#pragma unroll
-              for (int q = 0; q < N / 4; ++q)
-                d4[q] = make_float4(acc[u][4 * q], acc[u][4 * q + 1], acc[u][4 * q + 2], acc[u][4 * q + 3]);
-            } else {
-              reinterpret_cast<int4*>(dst_row)[idx] = pack_vec<T>(acc[u]);
-            }
-          }
+        const uint8_t* my_row = ey + (size_t)(lane < cnt ? crow : 0) * row_bytes;
+        bool ok;
+        if (p.partial_fp32 && !direct_out) {
+          ok = warp_weighted_sum_bulk<T, true>(my_row, cw, cnt, v_lo, v_hi, dst_row, stage, stage_u32, bar, parity, lane,
+                                               p.timeout_ns, p.status);
+        } else {
+          ok = warp_weighted_sum_bulk<T, false>(my_row, cw, cnt, v_lo, v_hi, dst_row, stage, stage_u32, bar, parity, lane,
+                                                p.timeout_ns, p.status);
+        }
+        if (!ok) {  // recorded as a timeout: the CTA-wide waits below will see it and give up together
+          warp_ok = false;
+          break;
         }
       } else if (piece == 0) {
         // the trip count is the same for every lane: the shuffles below need the whole warp
@@ -661,7 +725,19 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
       }
       const unsigned mask = __reduce_or_sync(0xffffffffu, dst >= 0 ? (1u << dst) : 0u);
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + (size_t)t * row_bytes;
-      if (vec16) {
+      if (vec16 && !p.partial_fp32) {
+        const int v_lo = piece * pv, v_hi = min(nv, (piece + 1) * pv);
+        const int cnt = __popc(mask);
+        if (cnt == 0) {  // nothing was delivered for this token: a defined (zero) row
+          for (int idx = v_lo + lane; idx < v_hi; idx += 32) reinterpret_cast<int4*>(orow)[idx] = make_int4(0, 0, 0, 0);
+          continue;
+        }
+        const int d = (int)__fns(mask, 0, lane + 1);  // lane c: the c-th owner in ascending rank order
+        const uint8_t* my_row = ret + ((uint64_t)(lane < cnt ? d : 0) * p.max_tokens + t) * ret_row_bytes;
+        if (!warp_weighted_sum_bulk<T, false>(my_row, 1.f, cnt, v_lo, v_hi, orow, stage, stage_u32, bar, parity, lane,
+                                              p.timeout_ns, p.status))
+          break;
+      } else if (vec16) {
         const int v_lo = piece * pv, v_hi = min(nv, (piece + 1) * pv);
         for (int v0 = v_lo; v0 < v_hi; v0 += 32 * CU) {
           float acc[CU][N];
@@ -814,9 +890,13 @@ int moe_dedup_combine_max_blocks(int device) {
   if (cached_device == device) return cached;
   int sms = 0, per_sm = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_dedup_combine_kernel<__nv_bfloat16>, kThreads, 0);
+  const int smem = kWarps * kStageBytes;
+  cudaFuncSetAttribute(moe_dedup_combine_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaFuncSetAttribute(moe_dedup_combine_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaFuncSetAttribute(moe_dedup_combine_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_dedup_combine_kernel<__nv_bfloat16>, kThreads, smem);
   int other = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&other, moe_dedup_combine_kernel<float>, kThreads, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&other, moe_dedup_combine_kernel<float>, kThreads, smem);
   per_sm = std::max(1, std::min(std::min(per_sm, other), 3));
   cached_device = device;
   cached = std::max(sms, 1) * per_sm;
@@ -847,11 +927,14 @@ cudaError_t launch_moe_dedup_dispatch(const MoeDedupDispatchParams& p, int grid,
 
 cudaError_t launch_moe_dedup_combine(const MoeDedupCombineParams& p, int grid, cudaStream_t stream) {
   if (p.k < 1 || p.k > 32 || p.world_size > kMaxWorldSize) return cudaErrorInvalidValue;
+  // the opt-in to this much dynamic shared memory was made by moe_dedup_combine_max_blocks(), which
+  // every caller needs first to size the grid
+  const size_t smem = (size_t)kWarps * kStageBytes;
   if (!force_cooperative()) {
     switch (p.dtype) {
-      case 0: moe_dedup_combine_kernel<__half><<<grid, kThreads, 0, stream>>>(p); break;
-      case 1: moe_dedup_combine_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p); break;
-      case 2: moe_dedup_combine_kernel<float><<<grid, kThreads, 0, stream>>>(p); break;
+      case 0: moe_dedup_combine_kernel<__half><<<grid, kThreads, smem, stream>>>(p); break;
+      case 1: moe_dedup_combine_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p); break;
+      case 2: moe_dedup_combine_kernel<float><<<grid, kThreads, smem, stream>>>(p); break;
       default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
@@ -865,7 +948,7 @@ cudaError_t launch_moe_dedup_combine(const MoeDedupCombineParams& p, int grid, c
     case 2: kernel = (const void*)moe_dedup_combine_kernel<float>; break;
     default: return cudaErrorInvalidValue;
   }
-  return cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(kThreads), args, 0, stream);
+  return cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(kThreads), args, smem, stream);
 }
 
 }  // namespace b200

@@ -57,6 +57,18 @@ __device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t sm
                ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y)
                : "memory");
 }
+// Untiled bulk copies: contiguous runs of bytes, both addresses 16-byte aligned, size a multiple
+// of 16.  Load: global -> shared, completion counted in bytes on an mbarrier of this CTA.  Store:
+// shared -> global (the destination may be a peer GPU's memory), tracked by bulk async-groups.
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most N of this thread's bulk groups are still READING their shared-memory source.
 template <int N>

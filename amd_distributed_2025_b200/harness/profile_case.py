@@ -14,7 +14,7 @@ Examples::
     python -m amd_distributed_2025_b200.harness.profile_case --kernel moe --experts 256 --topk 8 --hidden 7168 --tokens 128
     python -m amd_distributed_2025_b200.harness.profile_case --kernel fp8_gemm --m 4096 --n 4096 --k 4096
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --m 8192 --n 8192 --k 28672 --trace
+        -m amd_distributed_2025_b200.harness.profile_case --kernel gemm_rs --gemm-m 8192 --gemm-n 8192 --gemm-k 28672 --trace
 
 Under ``torch.distributed.run`` the gemm_rs case runs on all ranks (``--k`` is the global K, split
 evenly) and every rank prints its own line; ``--trace`` adds the in-kernel phase stamps.
@@ -54,9 +54,10 @@ def _host_time_us(fn, ws: int, iters: int = 20) -> float:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", choices=["gemm_rs", "moe", "fp8_gemm"], required=True)
-    ap.add_argument("--m", type=int, default=8192)
-    ap.add_argument("--n", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=4096)
+    # the long spellings are for torch.distributed.run, whose own parser trips over "--m"
+    ap.add_argument("--m", "--gemm-m", dest="m", type=int, default=8192)
+    ap.add_argument("--n", "--gemm-n", dest="n", type=int, default=4096)
+    ap.add_argument("--k", "--gemm-k", dest="k", type=int, default=4096)
     ap.add_argument("--staged", action="store_true", help="gemm_rs: run the multi-rank staging/reduction path on one GPU")
     ap.add_argument("--trace", action="store_true", help="print the in-kernel phase stamps of the last launch")
     ap.add_argument("--mode", default=None, help="moe: protocol, dedup (default) or direct")
@@ -106,8 +107,10 @@ def main(argv=None) -> int:
             tr = op.trace.cpu()
             tr = tr[tr[:, 0] > 0]
             t0 = tr[:, 0].min()
-            names = {1: "pipeline_ready", 4: "first_own_tile", 5: "peers_rows_arrived", 6: "last_own_tile_stored",
-                     2: "gemm_tiles_done", 3: "exit"}
+            fused = op.fuse_own if op.fuse_own is not None else ws <= 4
+            names = {1: "pipeline_ready", 2: "gemm_tiles_done", 3: "exit"}
+            names.update({4: "first_own_tile", 5: "peers_rows_arrived", 6: "last_own_tile_stored"} if fused else
+                         {5: "first_unit_complete_after_gemm", 6: "last_unit_reduced"})
             stamps = {}
             for col, name in names.items():
                 c = tr[:, col]
