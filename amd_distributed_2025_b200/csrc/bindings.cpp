@@ -236,6 +236,7 @@ class MoeDedupEngine {
     TORCH_CHECK(blk_hist_.scalar_type() == at::kInt && blk_hist_.is_contiguous(), "blk_hist must be contiguous int32");
   }
 
+  bool bulk_landing = true;  // rows cross NVLink as bulk copies through shared memory (else 16-byte stores)
   int64_t dispatch_epoch() const { return dispatch_epoch_; }
   int64_t combine_epoch() const { return combine_epoch_; }
   void set_timeout_ns(int64_t t) { timeout_ns_ = t; }
@@ -267,7 +268,8 @@ class MoeDedupEngine {
     c10::cuda::CUDAGuard guard(heap_->device());
     const int ws = heap_->world_size();
     const int n = (int)(T * k_);
-    const int max_blocks = b200::moe_dedup_dispatch_max_blocks(heap_->device(), (int)E_, n);
+    const int bulk = (bulk_landing && ws > 1 && (H_ * elem_) % 16 == 0) ? 1 : 0;
+    const int max_blocks = b200::moe_dedup_dispatch_max_blocks(heap_->device(), (int)E_, n, bulk);
     TORCH_CHECK(blk_hist_.numel() >= (int64_t)max_blocks * E_, "blk_hist scratch too small");
     b200::MoeDedupDispatchParams p;
     p.x = x.data_ptr();
@@ -285,6 +287,7 @@ class MoeDedupEngine {
     p.row_bytes = (uint32_t)(H_ * elem_);
     p.pieces = pieces_for((int)T, max_blocks, 1);
     p.rep_pieces = pieces_for((int)T, max_blocks, 12);
+    p.bulk_landing = bulk;
     p.fuse_scale = fuse_scale ? 1 : 0;
     p.scale = (float)scale;
     p.epoch = (uint64_t)(++dispatch_epoch_);
@@ -900,11 +903,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("forward", &MoeDedupEngine::forward)
       .def("set_trace", &MoeDedupEngine::set_trace, py::arg("dispatch_trace") = py::none(), py::arg("combine_trace") = py::none())
       .def("set_timeout_ns", &MoeDedupEngine::set_timeout_ns)
+      .def_readwrite("bulk_landing", &MoeDedupEngine::bulk_landing)
       .def_property_readonly("dispatch_epoch", &MoeDedupEngine::dispatch_epoch)
       .def_property_readonly("combine_epoch", &MoeDedupEngine::combine_epoch);
-  m.def("moe_dedup_dispatch_max_blocks", [](int device, int num_experts, int num_entries) {
+  m.def("moe_dedup_dispatch_max_blocks", [](int device, int num_experts, int num_entries, int bulk_landing) {
     c10::cuda::CUDAGuard guard(device);
-    return b200::moe_dedup_dispatch_max_blocks(device, num_experts, num_entries);
+    return b200::moe_dedup_dispatch_max_blocks(device, num_experts, num_entries, bulk_landing);
   });
 
   py::class_<GemmRsEngine, std::shared_ptr<GemmRsEngine>>(m, "GemmRsEngine")

@@ -106,6 +106,8 @@ struct MoeDedupDispatchParams {
   uint32_t row_bytes;
   int32_t pieces;            // a row is landed by this many warps (small problems)
   int32_t rep_pieces;        // a landed row is replicated by this many warps (evens out the warps' shares)
+  int32_t bulk_landing;      // 1: rows cross to the owners as bulk copies through shared memory (cp.async.bulk),
+                             // 0: as 16-byte stores from registers
   int32_t fuse_scale;        // 1: the replication pass also writes expert_y = expert_x * scale
   float scale;
   uint64_t epoch, timeout_ns;
@@ -140,7 +142,7 @@ struct MoeDedupCombineParams {
 };
 
 // Co-resident grid sizes (cooperative launches) for the current device.
-int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries);
+int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries, int bulk_landing);
 int moe_dedup_combine_max_blocks(int device);
 cudaError_t launch_moe_dedup_dispatch(const MoeDedupDispatchParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_moe_dedup_combine(const MoeDedupCombineParams& p, int grid, cudaStream_t stream);

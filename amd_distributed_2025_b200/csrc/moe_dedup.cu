@@ -49,6 +49,8 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMetaDim = 5;
 constexpr int kU = 8;  // 16-byte vectors per lane held in registers per chunk (4 KiB per warp)
+constexpr int kLandStage = 4096;  // bytes per landing stage; two stages per warp
+constexpr int kLandBytes = kWarps * 2 * kLandStage;  // dynamic shared memory of the landing stages per CTA
 
 struct Dst2 {
   int4* x;
@@ -230,10 +232,21 @@ __device__ __forceinline__ bool warp_weighted_sum_bulk(const uint8_t* row, float
 // and meet once on a grid barrier.
 template <typename T, bool SMALL>
 __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeDedupDispatchParams p) {
-  extern __shared__ int32_t smem_i32[];
+  // dynamic shared memory: [landing stages: kLandBytes, only with bulk landing] [int32 work arrays]
+  extern __shared__ __align__(128) uint8_t smem_dispatch[];
+  int32_t* smem_i32 = reinterpret_cast<int32_t*>(smem_dispatch + (p.bulk_landing ? kLandBytes : 0));
+  __shared__ uint64_t land_bars[kWarps];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  if (p.bulk_landing) {
+    if (tid == 0) {
+      for (int wi = 0; wi < kWarps; ++wi) ptx::mbar_init(ptx::smem_u32(&land_bars[wi]), 1);
+      ptx::fence_mbar_init();
+      ptx::fence_proxy_async_smem();
+    }
+    __syncthreads();
+  }
   const int E = p.num_experts;
   const int El = p.num_local_experts;
   const int k = p.k;
@@ -364,6 +377,10 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
 
   // ---- phase C: land every token once per destination rank --------------------------------
   // (token, piece) items: this warp's own tokens, or strided over all warps when SMALL
+  const uint32_t land_stage_u32 = ptx::smem_u32(smem_dispatch + (size_t)warp * 2 * kLandStage);
+  const uint32_t land_bar = ptx::smem_u32(&land_bars[warp]);
+  uint32_t land_parity = 0, land_chunks = 0;
+  bool land_ok = true;
   {
     const int item0 = SMALL ? gw : w_t0;
     const int item1 = SMALL ? T_tok * P : w_t1;
@@ -386,7 +403,35 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
         if ((mask >> d) & 1u) r.x = peer_ptr<int4>(p.peer_base[d], land_off);
         return r;
       };
-      if (vec16) {
+      if (vec16 && p.bulk_landing) {
+        // One lane drives the copies: a run of the row comes into a stage with one bulk load and
+        // leaves with one bulk store per destination; the second stage is loaded while the stores
+        // of the first drain, and no register or issue slot is tied up by NVLink back-pressure.
+        if (lane == 0 && land_ok) {
+          const uint8_t* src = xbytes + (size_t)t * p.row_bytes;
+          const int v_lo = piece * pv, v_hi = min(nv, (piece + 1) * pv);
+          for (int vc = v_lo; vc < v_hi; vc += kLandStage / 16) {
+            const uint32_t bytes = (uint32_t)min(kLandStage / 16, v_hi - vc) * 16u;
+            const uint32_t st = land_stage_u32 + (land_chunks & 1u) * kLandStage;
+            ptx::bulk_wait_group_read<1>();  // the stores that used this stage two runs ago have read it
+            ptx::mbar_arrive_expect_tx(land_bar, bytes);
+            ptx::bulk_load(st, src + (size_t)vc * 16, bytes, land_bar);
+            if (!mbar_wait_bounded(land_bar, land_parity, p.timeout_ns, p.status, PHASE_MOE_DATA)) {
+              land_ok = false;
+              break;
+            }
+            land_parity ^= 1u;
+            ptx::fence_proxy_async_smem();
+            for (int j = 0; j < p.world_size - 1; ++j) {
+              const Dst2 d = dst_of(j);
+              if (d.x != nullptr) ptx::bulk_store(reinterpret_cast<uint8_t*>(d.x) + (size_t)vc * 16, st, bytes);
+            }
+            ptx::bulk_commit_group();
+            ++land_chunks;
+          }
+        }
+        __syncwarp();
+      } else if (vec16) {
         warp_fanout<T, false>(reinterpret_cast<const int4*>(xbytes + (size_t)t * p.row_bytes), piece * pv,
                               min(nv, (piece + 1) * pv), lane, p.world_size - 1, 0.f, dst_of);
       } else if (piece == 0) {
@@ -395,6 +440,11 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
       }
     }
   }
+  if (p.bulk_landing && lane == 0) {
+    ptx::bulk_wait_group<0>();  // this warp's bulk stores have been performed ...
+    asm volatile("fence.proxy.async.global;" ::: "memory");  // ... and are ordered before the flag stores below
+  }
+  __syncwarp();
   stamp(p.trace, 2);
 
   // ---- phase D: counts of all ranks -> final slots; metadata, row lists, weights, marks -----
@@ -825,9 +875,10 @@ bool force_cooperative() {
   return on;
 }
 
-size_t dispatch_smem(bool small, int num_entries, int num_experts) {
-  if (small) return ((size_t)((num_entries + 31) & ~31) + 2 * (size_t)num_experts) * sizeof(int32_t);
-  return (size_t)(kWarps + 2) * num_experts * sizeof(int32_t);
+size_t dispatch_smem(bool small, int num_entries, int num_experts, bool bulk_landing) {
+  const size_t stages = bulk_landing ? (size_t)kLandBytes : 0;
+  if (small) return stages + ((size_t)((num_entries + 31) & ~31) + 2 * (size_t)num_experts) * sizeof(int32_t);
+  return stages + (size_t)(kWarps + 2) * num_experts * sizeof(int32_t);
 }
 
 template <typename T, bool SMALL>
@@ -862,26 +913,27 @@ int dispatch_occupancy(bool small, size_t smem) {
 
 }  // namespace
 
-int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries) {
+int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries, int bulk_landing) {
   // Occupancy of the bf16 instantiation stands for all three (same code up to conversions).
-  struct Key { int device, experts, small_entries; int blocks; };
+  struct Key { int device, experts, small_entries, bulk; int blocks; };
   static thread_local Key cache[8];
   static thread_local int used = 0;
   const bool small = dedup_small(num_entries, num_experts);
   const int small_entries = small ? ((num_entries + 31) & ~31) : -1;
   for (int i = 0; i < used; ++i)
-    if (cache[i].device == device && cache[i].experts == num_experts && cache[i].small_entries == small_entries)
+    if (cache[i].device == device && cache[i].experts == num_experts && cache[i].small_entries == small_entries &&
+        cache[i].bulk == bulk_landing)
       return cache[i].blocks;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (sms <= 0) sms = 1;
-  const size_t smem = dispatch_smem(small, num_entries, num_experts);
+  const size_t smem = dispatch_smem(small, num_entries, num_experts, bulk_landing != 0);
   int per_sm = dispatch_occupancy<__nv_bfloat16>(small, smem);
   if (per_sm < 1) per_sm = 1;
   // the large kernel sums one histogram row per CTA: more than one CTA per SM does not pay there
   const int blocks = sms * (small ? std::min(per_sm, 2) : 1);
   Key& slot = cache[used < 8 ? used++ : 7];
-  slot = {device, num_experts, small_entries, blocks};
+  slot = {device, num_experts, small_entries, bulk_landing, blocks};
   return blocks;
 }
 
@@ -907,7 +959,7 @@ cudaError_t launch_moe_dedup_dispatch(const MoeDedupDispatchParams& p, int grid,
   const int n = p.num_tokens * p.k;
   if (p.k < 1 || p.k > 32 || p.world_size > kMaxWorldSize || p.num_tokens > p.max_tokens) return cudaErrorInvalidValue;
   const bool small = dedup_small(n, p.num_experts);
-  const size_t smem = dispatch_smem(small, n, p.num_experts);
+  const size_t smem = dispatch_smem(small, n, p.num_experts, p.bulk_landing != 0);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (small) {
     switch (p.dtype) {

@@ -146,6 +146,8 @@ class MoEAllToAll:
                 cfg.in_dtype, self.partial_fp32, [self.ws.offset(nm) for nm in names], self.expert_y, self._blk_hist,
                 self._route, self.expert_num_tokens, self.ws.wait_limit_ns,
             )
+            # B200_MOE_LANDING=lanes: rows cross NVLink as 16-byte stores from registers instead of bulk copies
+            self.engine.bulk_landing = os.environ.get("B200_MOE_LANDING", "bulk").strip().lower() != "lanes"
         self.trace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
     def _guard(self) -> None:
