@@ -846,6 +846,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                                   at::cuda::getCurrentCUDAStream()),
                         "barrier launch");
            })
+      .def("link_probe",
+           [](SymmHeap& h, int peer, int64_t src_offset, int64_t dst_offset, int64_t bytes, int mode, int chunk, int grid,
+              int64_t timeout_ns) {
+             c10::cuda::CUDAGuard guard(h.device());
+             cuda_check(b200::launch_link_probe(h, peer, (uint64_t)src_offset, (uint64_t)dst_offset, (uint64_t)bytes, mode,
+                                                chunk, grid, (uint64_t)timeout_ns, at::cuda::getCurrentCUDAStream()),
+                        "link_probe launch");
+           })
       .def("wait_selftest", [](SymmHeap& h, int slot, int64_t want, int64_t timeout_ns) {
         c10::cuda::CUDAGuard guard(h.device());
         cuda_check(b200::launch_wait_selftest(h, slot, (uint64_t)want, (uint64_t)timeout_ns,

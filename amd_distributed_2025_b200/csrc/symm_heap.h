@@ -77,4 +77,10 @@ cudaError_t launch_symm_barrier(const SymmHeap& heap, uint64_t epoch, uint64_t t
 cudaError_t launch_wait_selftest(const SymmHeap& heap, int slot, uint64_t want, uint64_t timeout_ns,
                                  cudaStream_t stream);
 
+// Peer-store bandwidth probe (link_probe.cu): copies `bytes` from this rank's slab at
+// src_offset into rank `peer`'s slab at dst_offset with 16-byte stores (mode 0) or bulk
+// copies of `chunk` bytes through shared memory (mode 1), and ends with a system-scope fence.
+cudaError_t launch_link_probe(const SymmHeap& heap, int peer, uint64_t src_offset, uint64_t dst_offset, uint64_t bytes,
+                              int mode, int chunk, int grid, uint64_t timeout_ns, cudaStream_t stream);
+
 }  // namespace b200
