@@ -211,8 +211,8 @@ class MoeDedupEngine {
     TORCH_CHECK(heap_->peers_open(), "symmetric heap: peers are not mapped yet");
     const int ws = heap_->world_size();
     TORCH_CHECK(E_ > 0 && E_ % ws == 0, "num_experts must be divisible by world_size");
-    TORCH_CHECK(k_ >= 1 && k_ <= 32, "experts_per_token must be in 1..32");
-    TORCH_CHECK(offsets.size() == 9, "expected 9 region offsets");
+    TORCH_CHECK(k_ >= 1 && k_ <= 15, "experts_per_token must be in 1..15 (one 32-lane store per token record)");
+    TORCH_CHECK(offsets.size() == 7, "expected 7 region offsets");
     El_ = E_ / ws;
     TORCH_CHECK(El_ * max_recv_ < (1ll << 31), "expert buffer has too many rows for 32-bit row ids");
     lay_.off_counts = (uint64_t)offsets[0];
@@ -220,10 +220,9 @@ class MoeDedupEngine {
     lay_.off_expert_meta = (uint64_t)offsets[2];
     lay_.off_expert_y = (uint64_t)offsets[3];
     lay_.off_land = (uint64_t)offsets[4];
-    lay_.off_tok_rows = (uint64_t)offsets[5];
-    lay_.off_tok_w = (uint64_t)offsets[6];
-    lay_.off_tok_mark = (uint64_t)offsets[7];
-    lay_.off_ret = (uint64_t)offsets[8];
+    lay_.off_tok_rec = (uint64_t)offsets[5];
+    lay_.off_ret = (uint64_t)offsets[6];
+    rec_ints_ = (int)((1 + 2 * k_ + 3) / 4 * 4);
     elem_ = (int64_t)c10::elementSize(dtype_);
     dtype_code_ = dtype_code(dtype_);
     TORCH_CHECK(route_.scalar_type() == at::kInt && route_.is_contiguous() && route_.numel() >= 2 * max_tokens_ * k_,
@@ -283,6 +282,7 @@ class MoeDedupEngine {
     p.rank = heap_->rank();
     p.max_recv = (int32_t)max_recv_;
     p.max_tokens = (int32_t)max_tokens_;
+    p.rec_ints = rec_ints_;
     p.dtype = dtype_code_;
     p.row_bytes = (uint32_t)(H_ * elem_);
     p.pieces = pieces_for((int)T, max_blocks, 1);
@@ -341,6 +341,7 @@ class MoeDedupEngine {
     p.rank = heap_->rank();
     p.max_recv = (int32_t)max_recv_;
     p.max_tokens = (int32_t)max_tokens_;
+    p.rec_ints = rec_ints_;
     p.dtype = dtype_code_;
     p.partial_fp32 = partial_fp32_ ? 1 : 0;
     p.weights_sent = weights_sent_ ? 1 : 0;
@@ -390,6 +391,7 @@ class MoeDedupEngine {
   int64_t E_, k_, H_, max_tokens_, max_recv_, El_ = 0, elem_ = 2;
   at::ScalarType dtype_;
   int dtype_code_ = 0;
+  int rec_ints_ = 4;
   bool partial_fp32_;
   b200::MoeDedupLayout lay_;
   at::Tensor expert_y_, blk_hist_, route_, expert_num_tokens_;

@@ -91,9 +91,9 @@ struct MoeDedupLayout {
   uint64_t off_expert_meta;  // int32 [E_local][max_recv][5]
   uint64_t off_expert_y;     // dtype [E_local][max_recv][hidden]
   uint64_t off_land;         // dtype [world][max_tokens][hidden]: row (s, t) = token t of rank s
-  uint64_t off_tok_rows;     // int32 [world][max_tokens][k]: final row of entry k on this rank, or -1
-  uint64_t off_tok_w;        // float [world][max_tokens][k]: routing weight of that entry
-  uint64_t off_tok_mark;     // uint32 [world][max_tokens]: low word of the dispatch epoch that landed (s, t)
+  uint64_t off_tok_rec;      // int32 [world][max_tokens][rec_ints]: one record per (source s, token t), written by
+                             // the sender with ONE coalesced store: [0] low word of the dispatch epoch that landed
+                             // it, [1, 1+k) final row of entry k on this rank or -1, [1+k, 1+2k) its routing weight
   uint64_t off_ret;          // dtype or float [world][max_tokens][hidden]: row (d, t) = owner d's partial of my token t
 };
 
@@ -102,6 +102,7 @@ struct MoeDedupDispatchParams {
   const int32_t* indices;    // [T, k]
   const float* weights;      // [T, k] or nullptr (then combine sends them)
   int32_t num_tokens, k, num_experts, num_local_experts, world_size, rank, max_recv, max_tokens;
+  int32_t rec_ints;          // int32 words per (source, token) record: 1 + 2k rounded up to a multiple of 4
   int32_t dtype;             // 0 = fp16, 1 = bf16, 2 = fp32
   uint32_t row_bytes;
   int32_t pieces;            // a row is landed by this many warps (small problems)
@@ -117,7 +118,7 @@ struct MoeDedupDispatchParams {
   int32_t* blk_hist;         // [grid][num_experts] (large kernel only)
   int2* route;               // [T*k] (owner rank, row) or (-1, -1)
   int32_t* expert_num_tokens;
-  uint32_t* sync_counters;   // [0] grid barrier, [1] finished CTAs
+  uint32_t* sync_counters;   // [0] grid barrier, [1] finished CTAs, [4] CTAs that have published their count rows
   StatusBlock* status;
   uint64_t* trace;           // optional [8] globaltimer stamps of CTA 0: start, counted, rows issued,
                              // counts arrived, metadata stored, all sources delivered, replicated, (max) exit
@@ -129,6 +130,7 @@ struct MoeDedupCombineParams {
   const int2* route;         // from dispatch
   const void* expert_y;      // this rank's expert outputs, dispatch layout (any local tensor)
   int32_t num_tokens, k, hidden, num_local_experts, world_size, rank, max_recv, max_tokens;
+  int32_t rec_ints;
   int32_t dtype;
   int32_t partial_fp32;      // return rows travel as fp32 instead of dtype
   int32_t weights_sent;      // dispatch already delivered the weights

@@ -373,6 +373,16 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     __threadfence_system();
     for (int dst = blockIdx.x; dst < p.world_size; dst += G)
       st_release_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_COUNTS, p.rank), p.epoch);
+    if (!SMALL) atomicAdd(&p.sync_counters[4], 1u);
+  }
+  if (!SMALL && p.world_size > 1) {
+    // The count rows must leave before the first row does: a GPU's stores to all its peers share
+    // one way out, and a few hundred bytes queued behind megabytes bound for a busy peer arrive
+    // when those have drained -- far too late for the peers that wait for them.
+    if (tid == 0)
+      wait_u32_ge(&p.sync_counters[4], (uint32_t)min(p.world_size, G), p.timeout_ns, p.status, PHASE_GRID_BARRIER, -1,
+                  (int)blockIdx.x, false);
+    __syncthreads();
   }
 
   // ---- phase C: land every token once per destination rank --------------------------------
@@ -508,29 +518,28 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
           record_status(p.status, STATUS_BAD_INDEX, PHASE_NONE, dst, t * k + lane, p.epoch, (uint64_t)(int64_t)slot);
         }
       }
-      if (lane < k) {
-        p.route[(size_t)t * k + lane] = make_int2(row >= 0 ? dst : -1, row);
-        if (row >= 0) {
-          int32_t* m = peer_ptr<int32_t>(p.peer_base[dst], p.layout.off_expert_meta) + (size_t)row * kMetaDim;
-          m[0] = e;
-          m[1] = p.rank;
-          m[2] = t;
-          m[3] = lane;
-          m[4] = 0;
-        }
-      }
+      if (lane < k) p.route[(size_t)t * k + lane] = make_int2(row >= 0 ? dst : -1, row);
       const float w = (p.weights != nullptr && lane < k) ? p.weights[(size_t)t * k + lane] : 0.f;
       unsigned mask = __reduce_or_sync(0xffffffffu, e >= 0 ? (1u << dst) : 0u);
-      const uint64_t rec = (uint64_t)p.rank * p.max_tokens + t;
+      // The record of (this rank, t) on every destination: lane 0 carries the mark, lanes 1..k the
+      // final rows, lanes k+1..2k the weights -- one coalesced store per destination.  (The 5-int
+      // metadata rows of the reference layout are written by the owner when it replicates.)
+      const int from = lane == 0 ? 0 : (lane <= k ? lane - 1 : lane - 1 - k);
+      const int row_f = __shfl_sync(0xffffffffu, row, from);
+      const int dst_f = __shfl_sync(0xffffffffu, dst, from);
+      const float w_f = __shfl_sync(0xffffffffu, w, from);
+      const int words = p.weights != nullptr ? 1 + 2 * k : 1 + k;
+      const uint64_t rec = ((uint64_t)p.rank * p.max_tokens + t) * p.rec_ints;
       while (mask) {
         const int d = __ffs(mask) - 1;
         mask &= mask - 1;
-        const uint64_t base = p.peer_base[d];
-        if (lane < k) {
-          peer_ptr<int32_t>(base, p.layout.off_tok_rows)[rec * k + lane] = (dst == d) ? row : -1;
-          if (p.weights != nullptr) peer_ptr<float>(base, p.layout.off_tok_w)[rec * k + lane] = (dst == d) ? w : 0.f;
+        if (lane < words) {
+          int32_t v;
+          if (lane == 0) v = (int32_t)epoch32;
+          else if (lane <= k) v = (dst_f == d) ? row_f : -1;
+          else v = __float_as_int((dst_f == d) ? w_f : 0.f);
+          peer_ptr<int32_t>(p.peer_base[d], p.layout.off_tok_rec)[rec + lane] = v;
         }
-        if (lane == 0) peer_ptr<uint32_t>(base, p.layout.off_tok_mark)[rec] = epoch32;
       }
     }
   }
@@ -544,6 +553,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
       }
       p.sync_counters[0] = 0;
       p.sync_counters[1] = 0;
+      p.sync_counters[4] = 0;
     }
   }
 
@@ -551,8 +561,8 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   const uint8_t* land = peer_ptr<const uint8_t>(my_base, p.layout.off_land);
   uint8_t* ex = peer_ptr<uint8_t>(my_base, p.layout.off_expert_x);
   uint8_t* ey = reinterpret_cast<uint8_t*>(p.expert_y);
-  const int32_t* tok_rows = peer_ptr<const int32_t>(my_base, p.layout.off_tok_rows);
-  const uint32_t* tok_mark = peer_ptr<const uint32_t>(my_base, p.layout.off_tok_mark);
+  const int32_t* tok_rec = peer_ptr<const int32_t>(my_base, p.layout.off_tok_rec);
+  int32_t* meta = peer_ptr<int32_t>(my_base, p.layout.off_expert_meta);
   const int total_rows = El * p.max_recv;
   for (int j = 0; j < p.world_size && alive; ++j) {
     int s = p.rank + j;
@@ -564,16 +574,26 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
       const int t = item / PR;
       const int piece = item - t * PR;
       const uint64_t rec = (uint64_t)s * p.max_tokens + t;
-      if (__ldcg(tok_mark + rec) != epoch32) continue;
-      int row = -1;
-      if (lane < k) {
-        row = __ldcg(tok_rows + rec * k + lane);
-        if (row >= total_rows) {
-          record_status(p.status, STATUS_BAD_INDEX, PHASE_MOE_DATA, s, t, p.epoch, (uint64_t)(int64_t)row);
-          row = -1;
-        }
+      // lane 0 reads the mark, lanes 1..k the rows of the record: one load for the warp
+      int word = 0;
+      if (lane <= k) word = __ldcg(tok_rec + rec * p.rec_ints + lane);
+      if ((uint32_t)__shfl_sync(0xffffffffu, word, 0) != epoch32) continue;
+      int row = __shfl_down_sync(0xffffffffu, word, 1);  // lane kk < k: row of entry kk
+      if (lane >= k) row = -1;
+      if (row >= total_rows) {
+        record_status(p.status, STATUS_BAD_INDEX, PHASE_MOE_DATA, s, t, p.epoch, (uint64_t)(int64_t)row);
+        row = -1;
       }
       if (__ballot_sync(0xffffffffu, row >= 0) == 0) continue;
+      if (piece == 0 && row >= 0) {
+        // metadata row of the reference layout: (global expert, source rank, token, k, 0)
+        int32_t* m = meta + (size_t)row * kMetaDim;
+        m[0] = p.rank * El + row / p.max_recv;
+        m[1] = s;
+        m[2] = t;
+        m[3] = lane;
+        m[4] = 0;
+      }
       const uint8_t* src = (s == p.rank) ? xbytes + (size_t)t * p.row_bytes : land + rec * p.row_bytes;
       auto dst_of = [&](int kk) {
         const int r = __shfl_sync(0xffffffffu, row, kk);
@@ -649,11 +669,11 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
         w = __ldg(p.weights + (size_t)t * k + lane);
       }
       unsigned mask = __reduce_or_sync(0xffffffffu, dst >= 0 ? (1u << dst) : 0u);
-      const uint64_t rec = (uint64_t)p.rank * p.max_tokens + t;
+      const uint64_t rec = ((uint64_t)p.rank * p.max_tokens + t) * p.rec_ints + 1 + k;
       while (mask) {
         const int d = __ffs(mask) - 1;
         mask &= mask - 1;
-        if (lane < k) peer_ptr<float>(p.peer_base[d], p.layout.off_tok_w)[rec * k + lane] = (dst == d) ? w : 0.f;
+        if (lane < k) peer_ptr<float>(p.peer_base[d], p.layout.off_tok_rec)[rec + lane] = (dst == d) ? w : 0.f;
       }
     }
     if (last_cta_arrives(&p.sync_counters[2])) {
@@ -668,9 +688,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
   stamp(p.trace, 1);
 
   // ---- phase 1: per landed (source, token): fp32 sum over the local entries, one row back ----
-  const int32_t* tok_rows = peer_ptr<const int32_t>(my_base, p.layout.off_tok_rows);
-  const float* tok_w = peer_ptr<const float>(my_base, p.layout.off_tok_w);
-  const uint32_t* tok_mark = peer_ptr<const uint32_t>(my_base, p.layout.off_tok_mark);
+  const int32_t* tok_rec = peer_ptr<const int32_t>(my_base, p.layout.off_tok_rec);
   const uint8_t* ey = reinterpret_cast<const uint8_t*>(p.expert_y);
   const int total_rows = p.num_local_experts * p.max_recv;
   const bool direct_out = p.world_size == 1;  // the only owner is the source: write the result itself
@@ -682,16 +700,19 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_combine_kernel(const MoeDe
       const int t = item / P;
       const int piece = item - t * P;
       const uint64_t rec = (uint64_t)s * p.max_tokens + t;
-      if (__ldcg(tok_mark + rec) != mark32) continue;
-      int row = -1;
-      float w = 0.f;
-      if (lane < k) {
-        row = __ldcg(tok_rows + rec * k + lane);
-        w = __ldcg(tok_w + rec * k + lane);
-        if (row >= total_rows) {
-          record_status(p.status, STATUS_BAD_INDEX, PHASE_MOE_RETURN, s, t, p.epoch, (uint64_t)(int64_t)row);
-          row = -1;
-        }
+      // one load for the warp: lane 0 the mark, lanes 1..k the rows, lanes k+1..2k the weights
+      int word = 0;
+      if (lane <= 2 * k) word = __ldcg(tok_rec + rec * p.rec_ints + lane);
+      if ((uint32_t)__shfl_sync(0xffffffffu, word, 0) != mark32) continue;
+      int row = __shfl_sync(0xffffffffu, word, (lane + 1) & 31);
+      float w = __int_as_float(__shfl_sync(0xffffffffu, word, (lane + 1 + k) & 31));
+      if (lane >= k) {
+        row = -1;
+        w = 0.f;
+      }
+      if (row >= total_rows) {
+        record_status(p.status, STATUS_BAD_INDEX, PHASE_MOE_RETURN, s, t, p.epoch, (uint64_t)(int64_t)row);
+        row = -1;
       }
       // compact the valid entries to lanes 0..cnt-1, keeping ascending k
       const unsigned valid = __ballot_sync(0xffffffffu, row >= 0);

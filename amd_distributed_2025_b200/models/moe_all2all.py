@@ -68,9 +68,8 @@ def moe_slab_layout(cfg: MoEConfig, world_size: int, header_bytes: int, mode: st
     if mode == "dedup":
         toks = world_size * cfg.max_num_tokens
         lay.add("land", toks * cfg.hidden_dim * _DTYPE_SIZE[cfg.in_dtype])
-        lay.add("tok_rows", toks * cfg.experts_per_token * 4)
-        lay.add("tok_w", toks * cfg.experts_per_token * 4)
-        lay.add("tok_mark", toks * 4)
+        rec_ints = (1 + 2 * cfg.experts_per_token + 3) // 4 * 4  # mark, k rows, k weights, padded to 16 bytes
+        lay.add("tok_rec", toks * rec_ints * 4)
         lay.add("ret", toks * cfg.hidden_dim * (partial_bytes or _DTYPE_SIZE[cfg.out_dtype]))
     return lay
 
@@ -102,8 +101,8 @@ class MoEAllToAll:
         if partial_dtype not in (None, cfg.out_dtype, torch.float32):
             raise ValueError("partial_dtype must be the output type or float32")
         self.partial_fp32 = partial_dtype == torch.float32 and cfg.out_dtype != torch.float32
-        if cfg.experts_per_token > 32 and self.mode == "dedup":
-            raise ValueError("the dedup protocol handles at most 32 experts per token")
+        if cfg.experts_per_token > 15 and self.mode == "dedup":
+            raise ValueError("the dedup protocol handles at most 15 experts per token (use mode='direct')")
         self.monitor = monitor  # optional parallel.health.HealthMonitor: peers are checked before every launch
         self.cfg = cfg
         self.rank = rank
@@ -140,7 +139,7 @@ class MoEAllToAll:
         self._off_expert_y = self.ws.offset("expert_y")
         self.engine = None
         if self.mode == "dedup":
-            names = ("counts", "expert_x", "expert_meta", "expert_y", "land", "tok_rows", "tok_w", "tok_mark", "ret")
+            names = ("counts", "expert_x", "expert_meta", "expert_y", "land", "tok_rec", "ret")
             self.engine = ext.MoeDedupEngine(
                 self.ws.heap, cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens, self.max_recv,
                 cfg.in_dtype, self.partial_fp32, [self.ws.offset(nm) for nm in names], self.expert_y, self._blk_hist,
