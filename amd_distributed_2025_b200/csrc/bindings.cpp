@@ -235,6 +235,7 @@ class MoeDedupEngine {
     TORCH_CHECK(blk_hist_.scalar_type() == at::kInt && blk_hist_.is_contiguous(), "blk_hist must be contiguous int32");
   }
 
+  int64_t chunks = 4;        // chunks of a large dispatch (1 = all rows under one flag)
   bool bulk_landing = true;  // rows cross NVLink as bulk copies through shared memory (else 16-byte stores)
   int64_t dispatch_epoch() const { return dispatch_epoch_; }
   int64_t combine_epoch() const { return combine_epoch_; }
@@ -285,8 +286,12 @@ class MoeDedupEngine {
     p.rec_ints = rec_ints_;
     p.dtype = dtype_code_;
     p.row_bytes = (uint32_t)(H_ * elem_);
+    // Large transfers between GPUs go in chunks with their own "delivered" flags, so that the owners
+    // replicate one chunk while the next is still crossing the links.
+    const bool small = b200::moe_dedup_is_small(n, (int)E_);
+    p.chunks = (!small && ws > 1 && T * H_ * elem_ >= (int64_t)(8 << 20)) ? (int)chunks : 1;
     p.pieces = pieces_for((int)T, max_blocks, 1);
-    p.rep_pieces = pieces_for((int)T, max_blocks, 12);
+    p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, 12);
     p.bulk_landing = bulk;
     p.fuse_scale = fuse_scale ? 1 : 0;
     p.scale = (float)scale;
@@ -914,6 +919,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_trace", &MoeDedupEngine::set_trace, py::arg("dispatch_trace") = py::none(), py::arg("combine_trace") = py::none())
       .def("set_timeout_ns", &MoeDedupEngine::set_timeout_ns)
       .def_readwrite("bulk_landing", &MoeDedupEngine::bulk_landing)
+      .def_readwrite("chunks", &MoeDedupEngine::chunks)
       .def_property_readonly("dispatch_epoch", &MoeDedupEngine::dispatch_epoch)
       .def_property_readonly("combine_epoch", &MoeDedupEngine::combine_epoch);
   m.def("moe_dedup_dispatch_max_blocks", [](int device, int num_experts, int num_entries, int bulk_landing) {

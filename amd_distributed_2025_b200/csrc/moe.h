@@ -107,6 +107,8 @@ struct MoeDedupDispatchParams {
   uint32_t row_bytes;
   int32_t pieces;            // a row is landed by this many warps (small problems)
   int32_t rep_pieces;        // a landed row is replicated by this many warps (evens out the warps' shares)
+  int32_t chunks;            // the large kernel lands its tokens in this many chunks, each with its own
+                             // "delivered" flag, so that the owners replicate chunk c while c + 1 is in flight
   int32_t bulk_landing;      // 1: rows cross to the owners as bulk copies through shared memory (cp.async.bulk),
                              // 0: as 16-byte stores from registers
   int32_t fuse_scale;        // 1: the replication pass also writes expert_y = expert_x * scale
@@ -143,6 +145,8 @@ struct MoeDedupCombineParams {
   uint64_t* trace;           // optional [8]: start, weights exchanged, partials pushed, all partials arrived, (max) exit
 };
 
+// True when a problem of this size takes the barrier-free small dispatch kernel.
+bool moe_dedup_is_small(int num_entries, int num_experts);
 // Co-resident grid sizes (cooperative launches) for the current device.
 int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries, int bulk_landing);
 int moe_dedup_combine_max_blocks(int device);

@@ -49,6 +49,7 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMetaDim = 5;
 constexpr int kU = 8;  // 16-byte vectors per lane held in registers per chunk (4 KiB per warp)
+constexpr int kMaxChunks = 8;
 constexpr int kLandStage = 4096;  // bytes per landing stage; two stages per warp
 constexpr int kLandBytes = kWarps * 2 * kLandStage;  // dynamic shared memory of the landing stages per CTA
 
@@ -113,13 +114,6 @@ __device__ __forceinline__ bool cta_wait_all(uint64_t my_base, int row, uint64_t
   if ((int)threadIdx.x < world) {
     wait_flag_ge(flag_ptr(my_base, row, threadIdx.x), epoch, limit, st, phase, threadIdx.x, (int)blockIdx.x);
   }
-  __syncthreads();
-  return !status_timed_out(st);
-}
-
-__device__ __forceinline__ bool cta_wait_one(uint64_t my_base, int row, int src, uint64_t epoch, uint64_t limit,
-                                             StatusBlock* st, uint32_t phase) {
-  if (threadIdx.x == 0) wait_flag_ge(flag_ptr(my_base, row, src), epoch, limit, st, phase, src, (int)blockIdx.x);
   __syncthreads();
   return !status_timed_out(st);
 }
@@ -369,7 +363,13 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     }
   }
   __syncthreads();
+  const int C = SMALL ? 1 : max(1, min(p.chunks, kMaxChunks));  // chunks of this rank's tokens, each with its own DATA flag
   if (tid == 0 && (int)blockIdx.x < p.world_size) {
+    // how this rank cuts its tokens into chunks travels with the counts: epoch | chunks | grid | tokens
+    const uint64_t info = ((p.epoch & 0xffffffull) << 40) | ((uint64_t)C << 36) | ((uint64_t)(SMALL ? 0 : G) << 24) |
+                          (uint64_t)T_tok;
+    for (int dst = blockIdx.x; dst < p.world_size; dst += G)
+      st_relaxed_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_INFO, p.rank), info);
     __threadfence_system();
     for (int dst = blockIdx.x; dst < p.world_size; dst += G)
       st_release_sys(flag_ptr(p.peer_base[dst], FLAG_MOE_COUNTS, p.rank), p.epoch);
@@ -385,15 +385,45 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     __syncthreads();
   }
 
+  // Counts of all ranks -> where this rank's rows start in every expert buffer.  The small kernel
+  // does this after its rows have left (their flight hides the count exchange); the large one
+  // before its first chunk, because every chunk needs final slots for its records.
+  bool alive = true;
+  const int32_t* counts = peer_ptr<const int32_t>(my_base, p.layout.off_counts);  // [world][E]
+  auto await_counts = [&]() {
+    alive = cta_wait_all(my_base, FLAG_MOE_COUNTS, p.epoch, p.world_size, p.timeout_ns, p.status, PHASE_MOE_COUNTS);
+    stamp(p.trace, 3);
+    if (!alive) return;
+    for (int e = tid; e < E; e += kThreads) {
+      int lower = 0;
+      for (int s = 0; s < p.rank; ++s) lower += __ldcg(counts + (size_t)s * E + e);
+      s_base[e] += lower;
+    }
+    if (blockIdx.x == 0) {
+      for (int el = tid; el < El; el += kThreads) {
+        int total = 0;
+        for (int s = 0; s < p.world_size; ++s) total += __ldcg(counts + (size_t)s * E + p.rank * El + el);
+        p.expert_num_tokens[el] = min(total, p.max_recv);
+      }
+    }
+    __syncthreads();
+  };
+  if (!SMALL) await_counts();
+
   // ---- phase C: land every token once per destination rank --------------------------------
   // (token, piece) items: this warp's own tokens, or strided over all warps when SMALL
   const uint32_t land_stage_u32 = ptx::smem_u32(smem_dispatch + (size_t)warp * 2 * kLandStage);
   const uint32_t land_bar = ptx::smem_u32(&land_bars[warp]);
   uint32_t land_parity = 0, land_chunks = 0;
   bool land_ok = true;
+  const int w_len = w_t1 - w_t0;
+  for (int c = 0; c < C; ++c) {
+  // chunk c of this warp's tokens: those with (i * C) / w_len == c, i counted from w_t0
+  const int c_t0 = w_t0 + (c * w_len + C - 1) / C;
+  const int c_t1 = w_t0 + ((c + 1) * w_len + C - 1) / C;
   {
-    const int item0 = SMALL ? gw : w_t0;
-    const int item1 = SMALL ? T_tok * P : w_t1;
+    const int item0 = SMALL ? gw : c_t0;
+    const int item1 = SMALL ? T_tok * P : c_t1;
     const int step = SMALL ? W : 1;
     for (int item = item0; item < item1; item += step) {
       const int t = SMALL ? item / P : item;
@@ -457,27 +487,11 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   __syncwarp();
   stamp(p.trace, 2);
 
-  // ---- phase D: counts of all ranks -> final slots; metadata, row lists, weights, marks -----
-  bool alive = cta_wait_all(my_base, FLAG_MOE_COUNTS, p.epoch, p.world_size, p.timeout_ns, p.status, PHASE_MOE_COUNTS);
-  stamp(p.trace, 3);
-  const int32_t* counts = peer_ptr<const int32_t>(my_base, p.layout.off_counts);  // [world][E]
+  // ---- phase D: final slots of the chunk's entries; one record per (token, destination) ------
+  if (SMALL) await_counts();
   if (alive) {
-    for (int e = tid; e < E; e += kThreads) {
-      int lower = 0;
-      for (int s = 0; s < p.rank; ++s) lower += __ldcg(counts + (size_t)s * E + e);
-      s_base[e] += lower;
-    }
-    if (blockIdx.x == 0) {
-      for (int el = tid; el < El; el += kThreads) {
-        int total = 0;
-        for (int s = 0; s < p.world_size; ++s) total += __ldcg(counts + (size_t)s * E + p.rank * El + el);
-        p.expert_num_tokens[el] = min(total, p.max_recv);
-      }
-    }
-    __syncthreads();
-
-    const int item0 = SMALL ? gw : w_t0;
-    const int item1 = SMALL ? T_tok : w_t1;
+    const int item0 = SMALL ? gw : c_t0;
+    const int item1 = SMALL ? T_tok : c_t1;
     const int step = SMALL ? W : 1;
     for (int t = item0; t < item1; t += step) {
       int e = -1;
@@ -545,34 +559,72 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   }
   stamp(p.trace, 4);
 
-  // ---- phase E: every CTA has delivered -> tell the owners --------------------------------
-  if (last_cta_arrives(&p.sync_counters[1])) {
+  // ---- phase E: every CTA has delivered its part of the chunk -> tell the owners -------------
+  if (last_cta_arrives(&p.sync_counters[16 + c])) {
     if (tid == 0) {
       if (!status_timed_out(p.status)) {  // no CTA of this rank gave up: everything was stored
-        for (int d = 0; d < p.world_size; ++d) st_relaxed_sys(flag_ptr(p.peer_base[d], FLAG_MOE_DATA, p.rank), p.epoch);
+        const uint64_t done = (p.epoch << 8) | (uint64_t)(c + 1);
+        for (int d = 0; d < p.world_size; ++d) st_relaxed_sys(flag_ptr(p.peer_base[d], FLAG_MOE_DATA, p.rank), done);
       }
-      p.sync_counters[0] = 0;
-      p.sync_counters[1] = 0;
-      p.sync_counters[4] = 0;
+      p.sync_counters[16 + c] = 0;
+      if (c == C - 1) {
+        p.sync_counters[0] = 0;
+        p.sync_counters[4] = 0;
+      }
     }
   }
+  }  // chunks
 
-  // ---- phase F: replicate landed rows into the expert buffers, source by source ------------
+  // ---- phase F: replicate landed rows into the expert buffers, chunk by chunk, source by source
+  // A source's chunk c is complete when its DATA flag reaches (epoch << 8) | (c + 1); the chunks of
+  // the sources are replicated while their later chunks are still crossing the links.
   const uint8_t* land = peer_ptr<const uint8_t>(my_base, p.layout.off_land);
   uint8_t* ex = peer_ptr<uint8_t>(my_base, p.layout.off_expert_x);
   uint8_t* ey = reinterpret_cast<uint8_t*>(p.expert_y);
   const int32_t* tok_rec = peer_ptr<const int32_t>(my_base, p.layout.off_tok_rec);
   int32_t* meta = peer_ptr<int32_t>(my_base, p.layout.off_expert_meta);
   const int total_rows = El * p.max_recv;
+  // how every source cut its tokens (its info word is in place once its counts flag is)
+  __shared__ int src_T[kMaxWorldSize], src_G[kMaxWorldSize], src_C[kMaxWorldSize];
+  if (tid < p.world_size) {
+    const uint64_t info = ld_acquire_sys(flag_ptr(my_base, FLAG_MOE_INFO, tid));
+    const bool fresh = ((info >> 40) & 0xffffffull) == (p.epoch & 0xffffffull);
+    src_T[tid] = fresh ? min((int)(info & 0xffffffull), p.max_tokens) : 0;
+    src_G[tid] = fresh ? (int)((info >> 24) & 0xfffull) : 0;
+    src_C[tid] = fresh ? max(1, (int)((info >> 36) & 0xfull)) : 1;
+  }
+  __syncthreads();
+  int c_max = 1;
+  for (int s = 0; s < p.world_size; ++s) c_max = max(c_max, src_C[s]);
+  for (int c = 0; c < c_max && alive; ++c) {
   for (int j = 0; j < p.world_size && alive; ++j) {
     int s = p.rank + j;
     if (s >= p.world_size) s -= p.world_size;
-    alive = cta_wait_one(my_base, FLAG_MOE_DATA, s, p.epoch, p.timeout_ns, p.status, PHASE_MOE_DATA);
+    const int Cs = src_C[s];
+    if (c >= Cs) continue;
+    if (tid == 0)
+      wait_flag_ge(flag_ptr(my_base, FLAG_MOE_DATA, s), (p.epoch << 8) | (uint64_t)(c + 1), p.timeout_ns, p.status,
+                   PHASE_MOE_DATA, s, (int)blockIdx.x);
+    __syncthreads();
+    alive = !status_timed_out(p.status);
     if (!alive) break;
-    if (j == p.world_size - 1) stamp(p.trace, 5);
-    for (int item = gw; item < p.max_tokens * PR; item += W) {
+    if (c == c_max - 1 && j == p.world_size - 1) stamp(p.trace, 5);
+    // the source's partition of its tokens: CTA g owns tpc tokens, its warp w tpw of those
+    const int Ts = src_T[s];
+    const int Gs = max(src_G[s], 1);
+    const int s_tpc = (Ts + Gs - 1) / Gs;
+    const int s_tpw = (s_tpc + kWarps - 1) / kWarps;
+    for (int item = gw; item < Ts * PR; item += W) {
       const int t = item / PR;
       const int piece = item - t * PR;
+      if (Cs > 1) {
+        const int g = t / s_tpc;
+        const int off = t - g * s_tpc;
+        const int w = off / s_tpw;
+        const int i = off - w * s_tpw;
+        const int len = min(s_tpw, min(s_tpc, Ts - g * s_tpc) - w * s_tpw);  // tokens of that warp
+        if ((i * Cs) / len != c) continue;
+      }
       const uint64_t rec = (uint64_t)s * p.max_tokens + t;
       // lane 0 reads the mark, lanes 1..k the rows of the record: one load for the warp
       int word = 0;
@@ -614,6 +666,7 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
       }
     }
   }
+  }  // chunks
   stamp(p.trace, 6);
   if (p.trace != nullptr && tid == 0) atomicMax(reinterpret_cast<unsigned long long*>(p.trace + 7), global_timer_ns());
 }
@@ -933,6 +986,8 @@ int dispatch_occupancy(bool small, size_t smem) {
 }
 
 }  // namespace
+
+bool moe_dedup_is_small(int num_entries, int num_experts) { return dedup_small(num_entries, num_experts); }
 
 int moe_dedup_dispatch_max_blocks(int device, int num_experts, int num_entries, int bulk_landing) {
   // Occupancy of the bf16 instantiation stands for all three (same code up to conversions).

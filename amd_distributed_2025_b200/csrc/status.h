@@ -60,6 +60,7 @@ enum FlagRow : int {
   FLAG_RS_DONE = 4,
   FLAG_TEST = 5,
   FLAG_MOE_RET = 6,
+  FLAG_MOE_INFO = 7,   // per source: how it cut its tokens into chunks (not a flag anybody waits on)
   FLAG_ROWS = 8,
 };
 

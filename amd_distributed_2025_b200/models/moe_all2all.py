@@ -147,6 +147,8 @@ class MoEAllToAll:
             )
             # B200_MOE_LANDING=lanes: rows cross NVLink as 16-byte stores from registers instead of bulk copies
             self.engine.bulk_landing = os.environ.get("B200_MOE_LANDING", "bulk").strip().lower() != "lanes"
+            # B200_MOE_CHUNKS: chunks (1..8) a large dispatch is cut into so that replication overlaps the transfer
+            self.engine.chunks = max(1, min(8, int(os.environ.get("B200_MOE_CHUNKS", "4"))))
         self.trace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
     def _guard(self) -> None:
