@@ -289,7 +289,8 @@ class MoeDedupEngine {
     // Large transfers between GPUs go in chunks with their own "delivered" flags, so that the owners
     // replicate one chunk while the next is still crossing the links.
     const bool small = b200::moe_dedup_is_small(n, (int)E_);
-    p.chunks = (!small && ws > 1 && T * H_ * elem_ >= (int64_t)(8 << 20)) ? (int)chunks : 1;
+    // (pays when a rank's inbound link, not its memory, sets the pace: measured a loss on 2 ranks)
+    p.chunks = (!small && ws >= 4 && T * H_ * elem_ >= (int64_t)(8 << 20)) ? (int)chunks : 1;
     p.pieces = pieces_for((int)T, max_blocks, 1);
     p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, 12);
     p.bulk_landing = bulk;

@@ -614,17 +614,22 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
     const int Gs = max(src_G[s], 1);
     const int s_tpc = (Ts + Gs - 1) / Gs;
     const int s_tpw = (s_tpc + kWarps - 1) / kWarps;
-    for (int item = gw; item < Ts * PR; item += W) {
-      const int t = item / PR;
-      const int piece = item - t * PR;
-      if (Cs > 1) {
-        const int g = t / s_tpc;
-        const int off = t - g * s_tpc;
-        const int w = off / s_tpw;
-        const int i = off - w * s_tpw;
-        const int len = min(s_tpw, min(s_tpc, Ts - g * s_tpc) - w * s_tpw);  // tokens of that warp
-        if ((i * Cs) / len != c) continue;
-      }
+    // Dense numbering of the chunk's tokens: (source warp, position inside its share of the chunk,
+    // piece) -- so that consecutive items are live and every warp here gets its share of them.
+    const int max_sub = (s_tpw + Cs - 1) / Cs;
+    const int n_items = Gs * kWarps * max_sub * PR;
+    for (int item = gw; item < n_items; item += W) {
+      const int piece = item % PR;
+      const int q = item / PR;
+      const int sub = q % max_sub;
+      const int pair = q / max_sub;
+      const int g = pair / kWarps;
+      const int w = pair - g * kWarps;
+      const int len = min(s_tpw, min(s_tpc, Ts - g * s_tpc) - w * s_tpw);  // tokens of that source warp
+      if (len <= 0) continue;
+      const int i = (c * len + Cs - 1) / Cs + sub;
+      if (i >= ((c + 1) * len + Cs - 1) / Cs) continue;
+      const int t = g * s_tpc + w * s_tpw + i;
       const uint64_t rec = (uint64_t)s * p.max_tokens + t;
       // lane 0 reads the mark, lanes 1..k the rows of the record: one load for the warp
       int word = 0;
