@@ -16,6 +16,7 @@
 #include "gemm_rs.h"
 #include "host_ops.h"
 #include "host_shm_heap.h"
+#include "mcast_region.h"
 #include "moe.h"
 #include "status.h"
 #include "symm_heap.h"
@@ -947,6 +948,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("tma_store", &GemmRsEngine::tma_store)
       .def_readwrite("force_staged", &GemmRsEngine::force_staged)
       .def_readwrite("checked", &GemmRsEngine::checked);
+
+  py::class_<b200::McastRegion, std::shared_ptr<b200::McastRegion>>(m, "McastRegion")
+      .def(py::init([](int rank, int world_size, int64_t bytes, int device) {
+             return std::make_shared<b200::McastRegion>(rank, world_size, (uint64_t)bytes, device);
+           }),
+           py::arg("rank"), py::arg("world_size"), py::arg("bytes"), py::arg("device"))
+      .def_static("supported",
+                  [](int device) {
+                    std::string why;
+                    const bool ok = b200::McastRegion::supported(device, &why);
+                    return py::make_tuple(ok, why);
+                  })
+      .def("create_and_export", &b200::McastRegion::create_and_export)
+      .def("import_from", &b200::McastRegion::import_from)
+      .def("add_device", &b200::McastRegion::add_device)
+      .def("bind_and_map", &b200::McastRegion::bind_and_map)
+      .def("close", &b200::McastRegion::close)
+      .def_property_readonly("bytes", [](const b200::McastRegion& r) { return (int64_t)r.bytes(); })
+      .def_property_readonly("mapped", &b200::McastRegion::mapped)
+      .def_property_readonly("local_ptr", [](const b200::McastRegion& r) { return (int64_t)reinterpret_cast<uintptr_t>(r.local_ptr()); })
+      .def_property_readonly("mc_ptr", [](const b200::McastRegion& r) { return (int64_t)reinterpret_cast<uintptr_t>(r.mc_ptr()); })
+      .def("view",
+           [](b200::McastRegion& r, int64_t offset, std::vector<int64_t> shape, at::ScalarType dtype) {
+             int64_t numel = 1;
+             for (auto s : shape) numel *= s;
+             const int64_t nbytes = numel * (int64_t)c10::elementSize(dtype);
+             TORCH_CHECK(r.mapped() && offset >= 0 && (uint64_t)(offset + nbytes) <= r.bytes(), "view outside the region");
+             auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, r.device());
+             return at::from_blob(static_cast<uint8_t*>(r.local_ptr()) + offset, shape, opts);
+           },
+           py::arg("offset"), py::arg("shape"), py::arg("dtype"))
+      .def("reduce_selftest", [](b200::McastRegion& r, int64_t offset, at::Tensor out) {
+        TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.numel() % 8 == 0,
+                    "out must be a contiguous bf16 CUDA tensor with a multiple of 8 elements");
+        c10::cuda::CUDAGuard guard(r.device());
+        cuda_check(b200::launch_mcast_selftest(r, (uint64_t)offset, out.data_ptr(), (uint64_t)(out.numel() / 8),
+                                               at::cuda::getCurrentCUDAStream()),
+                   "mcast selftest launch");
+      });
 
   m.attr("FLAG_BARRIER") = (int)b200::FLAG_BARRIER;
   m.attr("FLAG_TEST") = (int)b200::FLAG_TEST;

@@ -242,3 +242,117 @@ class SymmetricWorkspace:
             self.heap.close_peers()
             dist.barrier(group=self.group)
         self.heap.close()
+
+
+class McastWorkspace:
+    """A region of device memory per rank, all bound into one NVLink multicast object (NVLS).
+
+    ``local`` views address this rank's own memory; ``mc_ptr`` is the multicast address, through
+    which ``multimem.ld_reduce`` returns sums formed inside NVSwitch.  Creation and ``close`` are
+    collective.  ``McastWorkspace.probe`` tells whether the device and driver offer multicast at
+    all; creation can still fail (no permission to pass descriptors between the ranks, no switch):
+    callers treat any exception as "not available here" and keep their peer-to-peer path.
+
+    A rank must not exit while its memory is bound and peers may still read through the
+    multicast address: call ``close(collective=True)`` on every rank while idle.  The reference
+    has no counterpart (its reduce-scatter is a library call, gemm-rs/reference.py:59).
+    """
+
+    @staticmethod
+    def probe(device: Optional[int] = None) -> Tuple[bool, str]:
+        from ..ops import _ext
+
+        ext = _ext.load()
+        dev = torch.cuda.current_device() if device is None else device
+        ok, why = ext.McastRegion.supported(dev)
+        return bool(ok), str(why)
+
+    def __init__(self, nbytes: int, *, rank: Optional[int] = None, world_size: Optional[int] = None, group=None):
+        from ..ops import _ext
+
+        ext = _ext.load()
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("a process group is required to share the multicast object")
+        self.group = group
+        self.world_size = world_size if world_size is not None else dist.get_world_size(group)
+        self.rank = rank if rank is not None else dist.get_rank(group)
+        dev = torch.cuda.current_device()
+        # every step is followed by an agreement on its outcome, so that no rank is left waiting for
+        # a peer that gave up
+        self.region = None
+        err = ""
+        try:
+            self.region = ext.McastRegion(self.rank, self.world_size, int(nbytes), dev)
+        except Exception as exc:  # noqa: BLE001
+            err = str(exc)
+        self._agree(err, "creating the region")
+        fd, err = -1, ""
+        if self.rank == 0:
+            try:
+                fd = self.region.create_and_export()
+            except Exception as exc:  # noqa: BLE001
+                err = str(exc)
+        shared: List[Optional[tuple]] = [None] * self.world_size
+        dist.all_gather_object(shared, (os.getpid(), fd, err), group=group)
+        root_pid, root_fd, root_err = shared[0]
+        if root_err:
+            self._fail(f"rank 0 could not create the multicast object: {root_err}")
+        err = ""
+        if self.rank != 0:
+            try:
+                self.region.import_from(root_pid, root_fd)
+            except Exception as exc:  # noqa: BLE001
+                err = str(exc)
+        self._agree(err, "importing the multicast object")
+        err = ""
+        try:
+            self.region.add_device()
+        except Exception as exc:  # noqa: BLE001
+            err = str(exc)
+        self._agree(err, "adding the devices")  # also the barrier the driver wants before any bind
+        err = ""
+        try:
+            self.region.bind_and_map()
+        except Exception as exc:  # noqa: BLE001
+            err = str(exc)
+        self._agree(err, "binding and mapping")
+        self.bytes = self.region.bytes
+        self._closed = False
+
+    def _agree(self, err: str, what: str) -> None:
+        errs: List[Optional[str]] = [None] * self.world_size
+        dist.all_gather_object(errs, err, group=self.group)
+        bad = {r: e for r, e in enumerate(errs) if e}
+        if bad:
+            self._fail(f"{what} failed on ranks {sorted(bad)}: {next(iter(bad.values()))}")
+
+    def _fail(self, message: str) -> None:
+        if self.region is not None:
+            try:
+                self.region.close()
+            except Exception:  # noqa: BLE001
+                pass
+            self.region = None
+        raise RuntimeError("NVLink multicast is not available here: " + message)
+
+    @property
+    def mc_ptr(self) -> int:
+        return self.region.mc_ptr
+
+    @property
+    def local_ptr(self) -> int:
+        return self.region.local_ptr
+
+    def view(self, offset: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        return self.region.view(offset, list(shape), dtype)
+
+    def close(self, collective: bool = True) -> None:
+        if self._closed or self.region is None:
+            return
+        self._closed = True
+        torch.cuda.synchronize()
+        if collective:
+            dist.barrier(group=self.group)  # nobody reads through the multicast address any more
+        self.region.close()
+        if collective:
+            dist.barrier(group=self.group)

@@ -189,3 +189,38 @@ def test_gemm_rs_multi_rank(ws):
         assert per_rank, "no shape ran"
         for r in per_rank:
             assert r["ok"], (r["shape"], r["msg"], r["rel"], r["outliers"])
+
+
+def _mcast_rank(rank, world_size):
+    """Multicast region: every rank fills its part with (rank + 1), the in-switch sum must be
+    1 + 2 + ... + world_size everywhere.  Reports "unavailable" where the box offers no NVLS."""
+    from amd_distributed_2025_b200.parallel.symm_mem import McastWorkspace
+
+    ok, why = McastWorkspace.probe()
+    if not ok:
+        return {"available": False, "why": why}
+    try:
+        ws = McastWorkspace(4 << 20, rank=rank, world_size=world_size)
+    except RuntimeError as exc:
+        return {"available": False, "why": str(exc)}
+    n = 1 << 16
+    ws.view(0, (n,), torch.bfloat16).fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    ws.region.reduce_selftest(0, out)
+    torch.cuda.synchronize()
+    want = float(world_size * (world_size + 1) // 2)
+    good = bool((out.float() == want).all())
+    torch.distributed.barrier()
+    ws.close(collective=True)
+    return {"available": True, "ok": good, "got": float(out[0]), "want": want}
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_multicast_region_sums_in_the_switch(ws):
+    res = run_ranks(_mcast_rank, ws, "nccl", (), 300.0)
+    if not all(r["available"] for r in res):
+        pytest.skip("NVLink multicast unavailable: " + "; ".join(sorted({r.get("why", "") for r in res if not r["available"]})))
+    for r in res:
+        assert r["ok"], r
