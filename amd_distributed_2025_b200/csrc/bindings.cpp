@@ -466,6 +466,8 @@ void gemm_rs(SymmHeap& heap, const at::Tensor& a, const at::Tensor& w, const c10
   g.force_staged = force_staged ? 1 : 0;
   g.checked = checked ? 1 : 0;
   g.stage_capacity = (uint64_t)stage_capacity;
+  g.nvls_local = 0;
+  g.nvls_mc = 0;
   if (trace.has_value() && trace->defined()) {
     TORCH_CHECK(trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 8 * 160,
                 "trace must be a contiguous int64 tensor with at least 1280 elements");
@@ -496,6 +498,13 @@ class GemmRsEngine {
 
   int64_t epoch() const { return epoch_; }
   void restart_epochs() { epoch_ = 0; }
+  // NVLS mode: stage in a multicast region that holds two parities of bf16 [M][N]; nullptr = back to peer stores
+  void set_mcast(std::shared_ptr<b200::McastRegion> region) {
+    TORCH_CHECK(!region || (region->mapped() && (int64_t)region->bytes() >= 2 * stage_bytes_),
+                "the multicast region must be mapped and hold two staging parities");
+    mcast_ = std::move(region);
+  }
+  bool nvls() const { return (bool)mcast_; }
   void set_trace(const c10::optional<at::Tensor>& trace) {
     trace_ = nullptr;
     trace_keep_ = at::Tensor();
@@ -576,6 +585,13 @@ class GemmRsEngine {
     g.force_staged = force_staged ? 1 : 0;
     g.checked = checked ? 1 : 0;
     g.stage_capacity = (uint64_t)stage_bytes_;
+    g.nvls_local = 0;
+    g.nvls_mc = 0;
+    if (mcast_ && plan.splits == 1 && ws > 1 && !force_staged) {
+      const uint64_t off = (uint64_t)parity * (uint64_t)stage_bytes_;
+      g.nvls_local = reinterpret_cast<uint64_t>(mcast_->local_ptr()) + off;
+      g.nvls_mc = reinterpret_cast<uint64_t>(mcast_->mc_ptr()) + off;
+    }
     cuda_check(b200::launch_gemm_rs(g, at::cuda::getCurrentCUDAStream()), "gemm_rs launch");
     return 0;
   }
@@ -602,6 +618,7 @@ class GemmRsEngine {
   uint64_t* trace_ = nullptr;
   at::Tensor trace_keep_;
   std::vector<PlanEntry> plans_;
+  std::shared_ptr<b200::McastRegion> mcast_;
 };
 
 // ------------------------------------------------------------------------ fp8 GEMM ----
@@ -938,6 +955,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("plan", &GemmRsEngine::plan)
       .def("set_trace", &GemmRsEngine::set_trace)
       .def("restart_epochs", &GemmRsEngine::restart_epochs)
+      .def("set_mcast", &GemmRsEngine::set_mcast)
+      .def_property_readonly("nvls", &GemmRsEngine::nvls)
       .def_property_readonly("epoch", &GemmRsEngine::epoch)
       .def_readwrite("max_ctas", &GemmRsEngine::max_ctas)
       .def_readwrite("block_n", &GemmRsEngine::block_n)

@@ -57,6 +57,8 @@ struct GemmRsArgs {
                     // staged like the others and reduced by all CTAs after the GEMM tiles
   int tma_store;    // 0 = per-lane staging stores only; otherwise TMA stores where the shape allows
   int force_staged; // 1 = stage and reduce even on a single rank (exercises the staged path on one GPU)
+  uint64_t nvls_local;  // NVLS mode (both non-zero): this parity's staging in this rank's own multicast-bound memory,
+  uint64_t nvls_mc;     // bf16 [M][N], and the same offset seen through the multicast address
   int checked;      // 1 = range-check every staging store against `stage_capacity` (record and skip on violation)
   uint64_t stage_capacity;  // bytes of one parity's staging region
 };

@@ -114,6 +114,9 @@ struct KernelParams {
   int direct;       // 1: one rank, K not sliced: tiles are written straight to `out`, nothing is staged
   int tma_store;    // 1: whole 32-row groups go to one owner and there are tensor maps for every owner:
                     // staged tiles leave through TMA stores instead of per-lane stores
+  int nvls;         // 1: every rank stages ALL its partial tiles in its own multicast-bound memory (layout
+                    // [M][N]); owners pull the sum through NVSwitch with multimem.ld_reduce
+  uint64_t nvls_local, nvls_mc;  // this parity's staging: own memory, and the multicast address
   int checked;      // 1: every staging store first proves that its owner and byte range lie inside the
                     // staging region of one parity; a violation is recorded (STATUS_BAD_INDEX) and skipped
   uint64_t stage_capacity;  // bytes of one parity's staging region
@@ -332,6 +335,50 @@ __device__ __forceinline__ void reduce_block(const KernelParams& p, const __nv_b
   }
 }
 
+// NVLS form: the partials of all ranks sit at the same offset of their own multicast-bound
+// staging ([M][N] bf16); one multimem.ld_reduce per 16 bytes returns their sum, formed in fp32
+// inside the switch and rounded once.  A bias that is added once goes on top (second rounding).
+__device__ __forceinline__ void reduce_block_nvls(const KernelParams& p, int r0, int row_lo, int c0, int vec_per_row,
+                                                  int item_lo, int items, int lane) {
+  constexpr int U = 4;
+  const __nv_bfloat16* mc = reinterpret_cast<const __nv_bfloat16*>(p.nvls_mc);
+  for (int base = item_lo + lane; base < items; base += 32 * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 32;
+      if (i < items) {
+        const size_t off = (size_t)(r0 + i / vec_per_row) * p.N + c0 + ((i % vec_per_row) << 3);
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "l"(mc + off)
+                     : "memory");
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 32;
+      if (i >= items) continue;
+      const int m = r0 + i / vec_per_row;
+      const int n = c0 + ((i % vec_per_row) << 3);
+      uint4 o = v[u];
+      if (p.bias != nullptr && !p.bias_at_source) {
+        const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + n);
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&bv);
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+        uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fb = __bfloat1622float2(hb[e]);
+          const float2 fv = __bfloat1622float2(hv[e]);
+          po[e] = pack_bf16x2(fmaf(fb.x, p.bias_scale, fv.x), fmaf(fb.y, p.bias_scale, fv.y));
+        }
+      }
+      *reinterpret_cast<uint4*>(p.out + (size_t)(m - row_lo) * p.N + n) = o;
+    }
+  }
+}
+
 // Same for a K-sliced problem, whose staging holds fp32 slices [world * splits][R][N].  The
 // slices of one rank are summed in fp32 and rounded to bf16 -- that is the rank's matmul
 // output in the reference -- the bias is added per rank in bf16 if the reference order was
@@ -516,7 +563,8 @@ __device__ __forceinline__ void reduce_staged_units(const KernelParams& p, int* 
       const int lo = cut * cut_items;
       const int hi = min(items, lo + cut_items);
       if (lo < hi) {
-        if (p.splits > 1) reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row, lo, hi, lane);
+        if (p.nvls) reduce_block_nvls(p, r0, row_lo, c0, vec_per_row, lo, hi, lane);
+        else if (p.splits > 1) reduce_block_sliced(p, reinterpret_cast<const float*>(stage), r0, row_lo, c0, vec_per_row, lo, hi, lane);
         else reduce_block(p, stage, r0, row_lo, c0, vec_per_row, lo, hi, lane);
       }
     }
@@ -805,7 +853,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           ptx::fence_proxy_async_smem();  // this lane's slab writes, for the async proxy
           __syncwarp();
           bool in_range = true;
-          if (p.checked) {
+          if (p.checked && !p.nvls) {
             const long long rl0 = (long long)m0 - (long long)owner0 * R;
             in_range = owner0 >= 0 && owner0 < p.world_size && rl0 >= 0 && rl0 + 32 <= R &&
                        ((uint64_t)(p.rank + 1) * R * p.N * 2ull) <= p.stage_capacity;
@@ -813,11 +861,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               record_status(p.status, STATUS_BAD_INDEX, PHASE_RS_PARTIALS, owner0, (int)(mb * p.n_tiles + nb), p.epoch, (uint64_t)m0);
           }
           if (lane == 0 && p.debug != 2 && in_range) {
-            const void* map = &stage_maps.m[p.debug == 1 ? p.rank : owner0];
+            // nvls: one map over this rank's own [M, N] staging; else the owner's block for this rank
+            const void* map = &stage_maps.m[p.nvls ? 0 : (p.debug == 1 ? p.rank : owner0)];
+            const int y = p.nvls ? m0 : m0 - owner0 * R;
 #pragma unroll
             for (int sub = 0; sub < C::kEpiCols / 64; ++sub) {
               const int x = n0 + half * cols_per_pass + sub * 64;
-              if (x < p.N) ptx::tma_store_2d(map, slab + sub * kSubBytes, x, m0 - owner0 * R);
+              if (x < p.N) ptx::tma_store_2d(map, slab + sub * kSubBytes, x, y);
             }
             ptx::bulk_commit_group();
           }
@@ -869,6 +919,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const int m = m0 + rr;
           const int n = n0 + half * cols_per_pass + cc * (sliced ? 4 : 8);
           if (m < p.M && n < p.N) {
+            if (p.nvls && !direct) {
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.nvls_local) + (size_t)m * p.N + n) = val;
+              continue;
+            }
             if (p.checked && !direct) {
               const int owner = m / R;
               const uint64_t elem = ((uint64_t)(p.rank * p.splits + split) * R + (uint64_t)(m - owner * R)) * p.N + n;
@@ -935,7 +989,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const int o_hi = m_hi / R;
           if (o_lo <= o_hi) {
             // device scope is enough (and much cheaper) when the only owner is this GPU
-            if (o_lo == p.rank && o_hi == p.rank) __threadfence();
+            if (o_lo == p.rank && o_hi == p.rank && !p.nvls) __threadfence();
             else __threadfence_system();
             const size_t base_index = ((size_t)mb * p.n_tiles + nb) * kEpilogueWarps;
             for (int o = o_lo; o <= o_hi; ++o) {
@@ -1143,11 +1197,26 @@ cudaError_t launch_typed(const GemmRsArgs& a, int sms, int splits, cudaStream_t 
   p.fuse_own = a.fuse_own;
   p.checked = a.checked;
   p.stage_capacity = a.stage_capacity;
+  // NVLS: bf16 partials only (K slices travel as fp32 and keep the peer-to-peer path), at least two ranks
+  p.nvls = (a.nvls_mc != 0 && a.nvls_local != 0 && a.world_size > 1 && splits == 1) ? 1 : 0;
+  p.nvls_local = a.nvls_local;
+  p.nvls_mc = a.nvls_mc;
+  if (p.nvls) {
+    // Everybody visits the tiles in the SAME order (no rotation), so that a tile is complete on all
+    // ranks at about the same time and its owner can pull it at once: the transfers spread over the
+    // whole run instead of piling up at its end.
+    p.m_start = 0;
+    p.fuse_own = 0;
+  }
   p.direct = (a.world_size == 1 && splits == 1 && !a.force_staged) ? 1 : 0;
   StageMaps maps;
   std::memset(&maps, 0, sizeof(maps));
   p.tma_store = 0;
-  if (a.world_size <= kMaxStageMaps && splits == 1 && !p.direct && p.rows_per_rank % 32 == 0 && a.tma_store != 0) {
+  if (p.nvls && a.tma_store != 0) {
+    p.tma_store = 1;
+    if (!make_tensor_map(&maps.m[0], reinterpret_cast<const void*>(a.nvls_local), (uint64_t)a.M, (uint64_t)a.N, 32))
+      return cudaErrorInvalidValue;
+  } else if (a.world_size <= kMaxStageMaps && splits == 1 && !p.direct && p.rows_per_rank % 32 == 0 && a.tma_store != 0) {
     p.tma_store = 1;
     for (int o = 0; o < a.world_size; ++o) {
       const uint8_t* base = reinterpret_cast<const uint8_t*>(a.peer_base[o]) + a.off_stage +

@@ -68,11 +68,14 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=128)
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--rs-mode", default=None, help="gemm_rs on several ranks: p2p (default) or nvls")
     ap.add_argument("--few-launches", action="store_true",
                     help="for a run under a profiler: one warm-up call, --iters timed calls, no host-time loop")
     ap.add_argument("--fuse-own", choices=["auto", "on", "off"], default="auto",
                     help="gemm_rs on several ranks: finish own tiles in their epilogue, or in a pass after the GEMM tiles")
     args = ap.parse_args(argv)
+    if args.rs_mode:
+        os.environ["B200_RS_MODE"] = args.rs_mode
     rank, ws = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if ws > 1:
@@ -99,7 +102,8 @@ def main(argv=None) -> int:
             op.trace.zero_()
         y = op(a, w, bias)
         torch.cuda.synchronize()
-        out.update(shape=[args.m, args.n, args.k], plan=dict(op.plan(args.m, args.n, k_local)), us=[t * 1e3 for t in times],
+        out.update(shape=[args.m, args.n, args.k], plan=dict(op.plan(args.m, args.n, k_local)), rs_mode=op.rs_mode,
+                   us=[t * 1e3 for t in times],
                    tflops_per_gpu=2.0 * args.m * args.n * k_local / min(times) / 1e9)
         if ws == 1:
             out["rel_err"] = oracle.relative_error(y, a.float() @ w.float().T + bias.float())

@@ -16,6 +16,7 @@ peer has started call ``n + 1`` and therefore finished reading parity ``n % 2``.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -23,7 +24,20 @@ import torch.distributed as dist
 
 from ..contract import GemmRsInput
 from ..parallel.baseline_nccl import gemm_rs_torch
-from ..parallel.symm_mem import SlabLayout, SymmetricWorkspace, checked, checked_guard_bytes
+from ..parallel.symm_mem import McastWorkspace, SlabLayout, SymmetricWorkspace, checked, checked_guard_bytes
+
+RS_MODES = ("p2p", "nvls")
+
+
+def default_rs_mode() -> str:
+    """``B200_RS_MODE``: "p2p" (default) stores partial tiles into the owners' memory over NVLink;
+    "nvls" keeps them in the producer's own multicast-bound memory and lets the owner pull their
+    sum through NVSwitch (``multimem.ld_reduce``).  Where the box offers no multicast, "nvls" falls
+    back to "p2p" (``GemmRS.rs_mode`` tells which one runs, ``GemmRS.rs_mode_note`` why)."""
+    mode = os.environ.get("B200_RS_MODE", "p2p").strip().lower()
+    if mode not in RS_MODES:
+        raise ValueError(f"B200_RS_MODE={mode!r}: expected one of {RS_MODES}")
+    return mode
 
 
 def gemm_rs_slab_layout(stage_bytes: int, counter_bytes: int, header_bytes: int, guard_bytes: int = 0) -> SlabLayout:
@@ -53,6 +67,7 @@ class GemmRS:
         device: Optional[torch.device] = None,
         wait_limit_ms: Optional[float] = None,
         monitor=None,
+        rs_mode: Optional[str] = None,
     ):
         from ..ops import _ext
 
@@ -82,6 +97,22 @@ class GemmRS:
             self.ws.wait_limit_ns,
         )
         self.engine.checked = checked()
+        # reduce-scatter transport: collective decision (every rank must end up in the same mode)
+        want = rs_mode or default_rs_mode()
+        if want not in RS_MODES:
+            raise ValueError(f"rs_mode {want!r}: expected one of {RS_MODES}")
+        self.rs_mode, self.rs_mode_note, self.mcast = "p2p", "", None
+        if want == "nvls" and self.world_size > 1:
+            ok, why = McastWorkspace.probe()
+            if not ok:
+                self.rs_mode_note = f"multicast not supported: {why}"
+            else:
+                try:
+                    self.mcast = McastWorkspace(2 * self.stage_bytes, rank=self.rank, world_size=self.world_size, group=group)
+                    self.engine.set_mcast(self.mcast.region)
+                    self.rs_mode = "nvls"
+                except RuntimeError as exc:  # raised on all ranks together (McastWorkspace agrees on every step)
+                    self.rs_mode_note = str(exc)
         self._fits = set()  # problem sizes already known to fit this workspace
         self.trace: Optional[torch.Tensor] = None  # int64 [160, 8]: per-CTA globaltimer stamps when set
 
@@ -161,6 +192,11 @@ class GemmRS:
         self.engine.restart_epochs()
 
     def close(self, collective: bool = False) -> None:
+        if self.mcast is not None:
+            # no rank may unbind its memory while a peer can still read through the multicast address
+            self.engine.set_mcast(None)
+            self.mcast.close(collective=collective and self.world_size > 1)
+            self.mcast = None
         self.ws.close(collective)
 
 

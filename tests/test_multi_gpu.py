@@ -140,9 +140,12 @@ def _gemm_check(rank, world_size, spec, seed, y, everyone):
     return bool(ok2 and rel < 5e-3), msg2, rel, outliers
 
 
-def _gemm_rank(rank, world_size, shapes, repeats):
+def _gemm_rank(rank, world_size, shapes, repeats, rs_mode="p2p"):
+    import os
+
     from amd_distributed_2025_b200.models import gemm_rs
 
+    os.environ["B200_RS_MODE"] = rs_mode  # read when the cached operator creates its workspace
     dev = torch.device("cuda", torch.cuda.current_device())
     out = []
     usable = [s for s in shapes if not (s[0] % world_size or s[2] % world_size or (s[2] // world_size) % 8)]
@@ -167,7 +170,9 @@ def _gemm_rank(rank, world_size, shapes, repeats):
                 pending.append((spec, seed, gemm_rs.custom_kernel(pending[0][3][rank]), pending[0][3]))
             torch.cuda.synchronize()
             try:
-                gemm_rs.get_op(m, n, k // world_size).check()
+                op = gemm_rs.get_op(m, n, k // world_size)
+                res["rs_mode"], res["rs_mode_note"] = op.rs_mode, op.rs_mode_note
+                op.check()
             except Exception as exc:  # noqa: BLE001
                 res["ok"], res["msg"] = False, str(exc)
                 break
@@ -183,12 +188,19 @@ def _gemm_rank(rank, world_size, shapes, repeats):
     return out
 
 
+@pytest.mark.parametrize("rs_mode", ["p2p", "nvls"])
 @pytest.mark.parametrize("ws", _world_sizes())
-def test_gemm_rs_multi_rank(ws):
-    for per_rank in run_ranks(_gemm_rank, ws, "nccl", (GEMM_SHAPES, 3), 900.0):
+def test_gemm_rs_multi_rank(ws, rs_mode):
+    """"p2p": partial tiles are stored into the owners' memory; "nvls": they stay with their
+    producer and the owner pulls their sum through NVSwitch.  Same results either way."""
+    results = run_ranks(_gemm_rank, ws, "nccl", (GEMM_SHAPES, 3, rs_mode), 900.0)
+    for per_rank in results:
         assert per_rank, "no shape ran"
         for r in per_rank:
             assert r["ok"], (r["shape"], r["msg"], r["rel"], r["outliers"])
+    ran = {r.get("rs_mode") for per_rank in results for r in per_rank}
+    if rs_mode == "nvls" and ran != {"nvls"}:
+        pytest.skip("NVLink multicast unavailable, the peer-to-peer path ran instead: " + results[0][0].get("rs_mode_note", ""))
 
 
 def _mcast_rank(rank, world_size):
