@@ -23,16 +23,25 @@ from .gemm_rs import gemm_rs_slab_layout
 from .moe_all2all import moe_slab_layout
 
 
+def _check_peers(monitor) -> None:
+    """With a monitor: post a heartbeat and raise ``PeerLostError`` if a peer announced its
+    departure or fell silent -- before this rank starts waiting for it."""
+    if monitor is not None:
+        monitor.beat()
+        monitor.assert_all_alive()
+
+
 class HostMoEAllToAll:
     """MoE dispatch / expert op / combine between CPU ranks through shared memory."""
 
     META_DIM = META_DIM
 
     def __init__(self, cfg: MoEConfig, rank: int, world_size: int, prefix: Optional[str] = None, group=None,
-                 wait_limit_ms: Optional[float] = None):
+                 wait_limit_ms: Optional[float] = None, monitor=None):
         from ..ops import _ext
 
         self.ext = _ext.load()
+        self.monitor = monitor  # optional parallel.health.HealthMonitor, consulted before every step that waits on peers
         if cfg.num_experts % world_size:
             raise ValueError("num_experts must divide by the world size")
         self.cfg, self.rank, self.world_size = cfg, rank, world_size
@@ -54,6 +63,7 @@ class HostMoEAllToAll:
         cfg = self.cfg
         if dp_x.dtype != cfg.in_dtype or dp_x.shape[1] != cfg.hidden_dim:
             raise ValueError("dp_x does not match the configuration")
+        _check_peers(self.monitor)
         status, route, num = self.ext.host_moe_dispatch(
             self.ws.heap, self._offsets, dp_x.contiguous(), indices, cfg.num_experts, self.max_recv, cfg.out_dtype,
             self.ws.next_epoch("moe_dispatch"), self.ws.wait_limit_ns,
@@ -81,6 +91,7 @@ class HostMoEAllToAll:
         if expert_y is not None and expert_y.data_ptr() != self.expert_y.data_ptr():
             self.expert_y.copy_(expert_y)
         cfg = self.cfg
+        _check_peers(self.monitor)
         status = self.ext.host_moe_combine(
             self.ws.heap, self._offsets, cfg.num_experts, self.max_recv, cfg.in_dtype, self.route,
             weights.to(torch.float32).contiguous(), out_tokens, self.ws.next_epoch("moe_combine"), self.ws.wait_limit_ns,
@@ -103,10 +114,11 @@ class HostGemmRS:
     partial row blocks go straight into the owners' staging slots."""
 
     def __init__(self, stage_bytes: int, rank: int, world_size: int, prefix: Optional[str] = None, group=None,
-                 wait_limit_ms: Optional[float] = None):
+                 wait_limit_ms: Optional[float] = None, monitor=None):
         from ..ops import _ext
 
         self.ext = _ext.load()
+        self.monitor = monitor
         self.rank, self.world_size, self.stage_bytes = rank, world_size, int(stage_bytes)
         layout = gemm_rs_slab_layout(self.stage_bytes, 0, self.ext.HEAP_HEADER_BYTES)
         self.ws = HostSymmetricWorkspace(layout, prefix or shared_prefix(group, "rs"), rank, world_size, wait_limit_ms)
@@ -115,6 +127,7 @@ class HostGemmRS:
                  bias_mode: str = "per_rank") -> torch.Tensor:
         if bias_mode not in ("per_rank", "once"):
             raise ValueError("bias_mode must be 'per_rank' or 'once'")
+        _check_peers(self.monitor)
         partial = torch.matmul(a, w.T)
         if bias is not None and bias_mode == "per_rank":
             partial = partial + bias  # the reference's order: every rank adds it before the reduction

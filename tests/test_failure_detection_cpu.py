@@ -96,3 +96,57 @@ def test_rank_that_never_joins_fails_rendezvous_within_timeout():
     assert not p.is_alive()
     assert q.get(timeout=5) != "joined"
     assert time.time() - t0 < 60
+
+
+def _operator_sees_departure(rank, world_size):
+    """The shared-memory operators consult the monitor themselves: after a rank has left between
+    steps, the survivors' next operator call raises ``PeerLostError`` on the host instead of
+    waiting for the departed rank's flags."""
+    from amd_distributed_2025_b200 import contract
+    from amd_distributed_2025_b200.models.host_ops import HostGemmRS, HostMoEAllToAll
+    from amd_distributed_2025_b200.parallel.health import HealthMonitor, PeerLostError, default_store
+
+    mon = HealthMonitor(default_store(), rank, world_size, stale_after_s=60.0)
+    cfg, data, _, _ = contract.make_moe_inputs(6, 2, 32, 8, 5, rank, world_size, device="cpu", dtype=torch.float32,
+                                               fixed_num_tokens=8)
+    layer = HostMoEAllToAll(cfg, rank, world_size, wait_limit_ms=20000, monitor=mon)
+    op = HostGemmRS(6 * 16 * 4, rank, world_size, wait_limit_ms=20000, monitor=mon)
+    a, w, bias = contract.make_gemm_rs_inputs(rank, world_size, 6, 16, 24, True, 3, device="cpu")
+    a, w, bias = a.float(), w.float(), bias.float()
+    y = layer.forward(data.x, data.indices, data.weights, 1 + rank)  # step 1: everybody is there
+    op(a, w, bias)
+    dist.barrier()
+    out = {"step1": list(y.shape), "left": False, "moe": None, "gemm": None}
+    if rank == world_size - 1:
+        mon.leave("planned exit after step 1")
+        out["left"] = True
+    else:
+        deadline = time.time() + 20
+        while time.time() < deadline and out["moe"] is None:
+            try:
+                mon.assert_all_alive()
+                time.sleep(0.05)
+                continue
+            except PeerLostError:
+                pass
+            try:
+                layer.forward(data.x, data.indices, data.weights, 1 + rank)
+                out["moe"] = "no error"
+            except PeerLostError as err:
+                out["moe"] = err.ranks
+            try:
+                op(a, w, bias)
+                out["gemm"] = "no error"
+            except PeerLostError as err:
+                out["gemm"] = err.ranks
+    dist.barrier()
+    layer.close()
+    op.close()
+    return out
+
+
+def test_shared_memory_operators_raise_peer_lost_from_the_call_itself():
+    res = run_ranks(_operator_sees_departure, 3, "gloo", (), 180.0)
+    assert res[2]["left"]
+    for r in res[:2]:
+        assert r["moe"] == [2] and r["gemm"] == [2], r
