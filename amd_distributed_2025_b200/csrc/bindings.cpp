@@ -237,6 +237,8 @@ class MoeDedupEngine {
   }
 
   int64_t chunks = 4;        // chunks of a large dispatch (1 = all rows under one flag)
+  int64_t chunk_min_ranks = 4;  // chunking starts at this world size ...
+  int64_t chunk_min_bytes = 8 << 20;  // ... and at this many bytes of token rows per rank
   bool bulk_landing = true;  // rows cross NVLink as bulk copies through shared memory (else 16-byte stores)
   int64_t dispatch_epoch() const { return dispatch_epoch_; }
   int64_t combine_epoch() const { return combine_epoch_; }
@@ -291,9 +293,9 @@ class MoeDedupEngine {
     // replicate one chunk while the next is still crossing the links.
     const bool small = b200::moe_dedup_is_small(n, (int)E_);
     // (pays when a rank's inbound link, not its memory, sets the pace: measured a loss on 2 ranks)
-    p.chunks = (!small && ws >= 4 && T * H_ * elem_ >= (int64_t)(8 << 20)) ? (int)chunks : 1;
+    p.chunks = (!small && ws >= chunk_min_ranks && T * H_ * elem_ >= chunk_min_bytes) ? (int)chunks : 1;
     p.pieces = pieces_for((int)T, max_blocks, 1);
-    p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, 12);
+    p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, 32);
     p.bulk_landing = bulk;
     p.fuse_scale = fuse_scale ? 1 : 0;
     p.scale = (float)scale;
@@ -939,6 +941,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_timeout_ns", &MoeDedupEngine::set_timeout_ns)
       .def_readwrite("bulk_landing", &MoeDedupEngine::bulk_landing)
       .def_readwrite("chunks", &MoeDedupEngine::chunks)
+      .def_readwrite("chunk_min_ranks", &MoeDedupEngine::chunk_min_ranks)
+      .def_readwrite("chunk_min_bytes", &MoeDedupEngine::chunk_min_bytes)
       .def_property_readonly("dispatch_epoch", &MoeDedupEngine::dispatch_epoch)
       .def_property_readonly("combine_epoch", &MoeDedupEngine::combine_epoch);
   m.def("moe_dedup_dispatch_max_blocks", [](int device, int num_experts, int num_entries, int bulk_landing) {

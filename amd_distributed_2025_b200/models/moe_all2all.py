@@ -149,6 +149,8 @@ class MoEAllToAll:
             self.engine.bulk_landing = os.environ.get("B200_MOE_LANDING", "bulk").strip().lower() != "lanes"
             # B200_MOE_CHUNKS: chunks (1..8) a large dispatch is cut into so that replication overlaps the transfer
             self.engine.chunks = max(1, min(8, int(os.environ.get("B200_MOE_CHUNKS", "4"))))
+            self.engine.chunk_min_ranks = int(os.environ.get("B200_MOE_CHUNK_MIN_RANKS", "4"))
+            self.engine.chunk_min_bytes = int(os.environ.get("B200_MOE_CHUNK_MIN_BYTES", str(8 << 20)))
         self.trace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
     def _guard(self) -> None:

@@ -43,8 +43,12 @@ def _moe_inputs(shape, it, world_size, dev):
             for r in range(world_size)]
 
 
-def _moe_rank(rank, world_size, shapes, repeats, modes):
+def _moe_rank(rank, world_size, shapes, repeats, modes, env=None):
+    import os
+
     from amd_distributed_2025_b200.models import moe_all2all
+
+    os.environ.update(env or {})  # knobs that a layer reads when it is created
 
     dev = torch.device("cuda", torch.cuda.current_device())
     out = []
@@ -99,6 +103,21 @@ def test_moe_dispatch_combine_multi_rank(ws):
         for r in per_rank:
             assert r["layout_ok"], (r["shape"], r["layout_msg"])
             assert r["ok"], (r["shape"], r["msg"])
+
+
+@pytest.mark.parametrize("ws", _world_sizes())
+def test_moe_chunked_dispatch_multi_rank(ws):
+    """The chunked form of the large dispatch (several "delivered" flags per source, replication
+    of chunk c while c + 1 is in flight), forced on for shapes and world sizes below its
+    thresholds, with 3 and with 4 chunks."""
+    big = [s for s in MOE_SHAPES if s[5] is not None]
+    for chunks in ("3", "4"):
+        env = {"B200_MOE_CHUNK_MIN_RANKS": "2", "B200_MOE_CHUNK_MIN_BYTES": "0", "B200_MOE_CHUNKS": chunks}
+        for per_rank in run_ranks(_moe_rank, ws, "nccl", (big, 3, ("dedup",), env), 900.0):
+            assert per_rank, "no shape ran"
+            for r in per_rank:
+                assert r["layout_ok"], (chunks, r["shape"], r["layout_msg"])
+                assert r["ok"], (chunks, r["shape"], r["msg"])
 
 
 GEMM_SHAPES = [
