@@ -596,35 +596,21 @@ __global__ void __launch_bounds__(kThreads) moe_dedup_dispatch_kernel(const MoeD
   __syncthreads();
   int c_max = 1;
   for (int s = 0; s < p.world_size; ++s) c_max = max(c_max, src_C[s]);
-  // Without chunks the sources are taken one by one as their flags come in (this rank's own rows
-  // first, while the others are still in flight).  With chunks the sources' chunk c arrives at
-  // about the same time: one wait for all of them, then the warps run through the sources without
-  // meeting again, so nobody idles at a barrier behind the warp with the longest token.
-  const bool by_source = c_max == 1;
+  // Chunk by chunk, and inside a chunk source by source as the flags come in (this rank's own rows
+  // first): the replication of one source's chunk overlaps the arrival of the next one's.
   for (int c = 0; c < c_max && alive; ++c) {
-  if (!by_source) {
-    if (tid < p.world_size && c < src_C[tid])
-      wait_flag_ge(flag_ptr(my_base, FLAG_MOE_DATA, tid), (p.epoch << 8) | (uint64_t)(c + 1), p.timeout_ns, p.status,
-                   PHASE_MOE_DATA, tid, (int)blockIdx.x);
-    __syncthreads();
-    alive = !status_timed_out(p.status);
-    if (!alive) break;
-    if (c == c_max - 1) stamp(p.trace, 5);
-  }
   for (int j = 0; j < p.world_size && alive; ++j) {
     int s = p.rank + j;
     if (s >= p.world_size) s -= p.world_size;
     const int Cs = src_C[s];
     if (c >= Cs) continue;
-    if (by_source) {
-      if (tid == 0)
-        wait_flag_ge(flag_ptr(my_base, FLAG_MOE_DATA, s), (p.epoch << 8) | (uint64_t)(c + 1), p.timeout_ns, p.status,
-                     PHASE_MOE_DATA, s, (int)blockIdx.x);
-      __syncthreads();
-      alive = !status_timed_out(p.status);
-      if (!alive) break;
-      if (j == p.world_size - 1) stamp(p.trace, 5);
-    }
+    if (tid == 0)
+      wait_flag_ge(flag_ptr(my_base, FLAG_MOE_DATA, s), (p.epoch << 8) | (uint64_t)(c + 1), p.timeout_ns, p.status,
+                   PHASE_MOE_DATA, s, (int)blockIdx.x);
+    __syncthreads();
+    alive = !status_timed_out(p.status);
+    if (!alive) break;
+    if (c == c_max - 1 && j == p.world_size - 1) stamp(p.trace, 5);
     // the source's partition of its tokens: CTA g owns tpc tokens, its warp w tpw of those
     const int Ts = src_T[s];
     const int Gs = max(src_G[s], 1);
