@@ -14,7 +14,7 @@ import os
 from typing import Dict, Optional
 
 FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-NVLINK_GBS_PER_DIR = 770.0  # measured peer copy per direction on this class of machine; 900 nominal
+NVLINK_GBS_PER_DIR = 700.0  # measured: a kernel's peer stores, per direction (harness/link_probe.py); 900 nominal
 
 
 def load_peaks(repo_root: Optional[str] = None) -> Dict[str, float]:
@@ -61,7 +61,9 @@ def moe_roofline_us(rows_out_remote: int, rows_in_remote: int, row_bytes: int, p
 
 def _moe_remote_rows(spec: Dict, world_size: int) -> Dict[str, int]:
     """Rows leaving / entering the busiest rank in one direction, from a seeded CPU draw of the
-    same routing distribution (the realised count matrix of a run differs only statistically)."""
+    same routing distribution (the realised count matrix of a run differs only statistically).
+    A token counts once per destination RANK, however many of its experts live there: that is
+    what the default protocol sends (csrc/moe_dedup.cu)."""
     import torch
 
     from .. import contract
@@ -76,8 +78,10 @@ def _moe_remote_rows(spec: Dict, world_size: int) -> Dict[str, int]:
             device="cpu", dtype=torch.float32, fixed_num_tokens=spec["tokens_per_rank"],
             routing=spec.get("routing", "uniform"), weights="rand", zipf_s=spec.get("zipf_s", 1.2),
         )
-        owners = torch.bincount((d.indices.to(torch.int64) // e_local).reshape(-1), minlength=world_size).tolist()
-        sent[r] = owners
+        owner = d.indices.to(torch.int64) // e_local  # [T, k]
+        hit = torch.zeros(owner.shape[0], world_size, dtype=torch.bool)
+        hit.scatter_(1, owner, True)
+        sent[r] = hit.sum(0).tolist()
     out_rows = max(sum(sent[r][o] for o in range(world_size) if o != r) for r in range(world_size))
     in_rows = max(sum(sent[r][o] for r in range(world_size) if r != o) for o in range(world_size))
     return {"out": out_rows, "in": in_rows}
@@ -102,8 +106,9 @@ def report(bench_line: Dict, peaks: Optional[Dict[str, float]] = None) -> Dict[s
             rows = _moe_remote_rows(spec, ws)
             row_bytes = spec["hidden_dim"] * 2
             link = moe_roofline_us(rows["out"], rows["in"], row_bytes, peaks)["roofline_us"]
-            # local floor: every routed row is written once and read once per phase, plus the expert op
-            local_bytes = 6.0 * spec["tokens_per_rank"] * spec["experts_per_token"] * row_bytes
+            # local floor: per entry one write each of expert_x and expert_y and one read of expert_y,
+            # per token one read of x and one write of the result
+            local_bytes = (3.0 * spec["experts_per_token"] + 2.0) * spec["tokens_per_rank"] * row_bytes
             roof = max(link, local_bytes / (peaks["hbm_gbs"] * 1e9) * 1e6)
         out[name] = {"measured_us": measured["us"], "roofline_us": roof, "fraction_of_roofline": roof / measured["us"]}
     return out
