@@ -171,3 +171,50 @@ def dedup_combine(owners, weights_per_rank, expert_y_per_rank, num_tokens: Seque
             for h in range(hidden):
                 out[src][t][h] += part[h]
     return out
+
+
+def dedup_chunk_tokens_sender(num_tokens: int, grid: int, chunks: int, warps: int = 8) -> List[List[int]]:
+    """Tokens a source rank sends under DATA-flag value ``c + 1``, for every chunk ``c``: each warp
+    cuts ITS OWN contiguous token range ``[t0, t1)`` into ``chunks`` parts, part ``c`` being
+    ``[t0 + ceil(c * len / C), t0 + ceil((c + 1) * len / C))`` (``moe_dedup_dispatch_kernel``,
+    landing loop)."""
+    out: List[List[int]] = [[] for _ in range(chunks)]
+    tpc = -(-num_tokens // grid)
+    tpw = -(-tpc // warps)
+    for b in range(grid):
+        c0 = min(num_tokens, b * tpc)
+        c1 = min(num_tokens, c0 + tpc)
+        for w in range(warps):
+            t0 = min(c1, c0 + w * tpw)
+            t1 = min(c1, t0 + tpw)
+            n = t1 - t0
+            for c in range(chunks):
+                out[c].extend(range(t0 + (c * n + chunks - 1) // chunks, t0 + ((c + 1) * n + chunks - 1) // chunks))
+    return out
+
+
+def dedup_chunk_tokens_receiver(num_tokens: int, grid: int, chunks: int, chunk: int, pieces: int = 1,
+                                warps: int = 8) -> List[Tuple[int, int]]:
+    """(token, piece) items an owner rank replicates for chunk ``chunk`` of a source that announced
+    ``(num_tokens, grid, chunks)`` in its info word: the dense numbering ``(source warp, position in
+    its share of the chunk, piece)`` of the replication loop.  ``grid == 0`` (the small kernel's
+    announcement) counts as one CTA."""
+    gs = max(grid, 1)
+    tpc = -(-num_tokens // gs)
+    tpw = -(-tpc // warps)
+    max_sub = -(-tpw // chunks)
+    items: List[Tuple[int, int]] = []
+    for item in range(gs * warps * max_sub * pieces):
+        piece = item % pieces
+        q = item // pieces
+        sub = q % max_sub
+        pair = q // max_sub
+        g, w = divmod(pair, warps)
+        n = min(tpw, min(tpc, num_tokens - g * tpc) - w * tpw)
+        if n <= 0:
+            continue
+        i = (chunk * n + chunks - 1) // chunks + sub
+        if i >= ((chunk + 1) * n + chunks - 1) // chunks:
+            continue
+        items.append((g * tpc + w * tpw + i, piece))
+    return items

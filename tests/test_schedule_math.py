@@ -102,3 +102,25 @@ def test_dedup_protocol_reproduces_oracle_layout_and_output(ws, E, k, T, grid):
     for r in range(ws):
         want = oracle.moe_expected_output(cfg, data[r], ws)
         assert torch.allclose(torch.tensor(out[r], dtype=torch.float32).reshape(-1, H), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("chunks", [1, 2, 3, 4, 7, 8])
+def test_dedup_chunks_sender_and_receiver_enumerate_the_same_tokens(chunks):
+    """What a source sends under chunk flag c must be exactly what the owner replicates after
+    seeing that flag, for token counts that divide neither the grid, the warps nor the chunks."""
+    for grid in (1, 2, 3, 37, 148, 296):
+        for tokens in (0, 1, 2, 7, 8, 9, 63, 64, 65, 127, 1000, 1023, 1024, 4095, 4096, 4097):
+            sent = sm.dedup_chunk_tokens_sender(tokens, grid, chunks)
+            assert sorted(t for part in sent for t in part) == list(range(tokens)), (tokens, grid, chunks)
+            for c in range(chunks):
+                for pieces in (1, 4):
+                    got = sm.dedup_chunk_tokens_receiver(tokens, grid, chunks, c, pieces=pieces)
+                    assert len(set(got)) == len(got)
+                    assert sorted(got) == sorted((t, p) for t in sent[c] for p in range(pieces)), (tokens, grid, chunks, c)
+
+
+def test_dedup_small_kernel_announcement_covers_every_token():
+    """The small kernel announces grid 0 and one chunk: the owner must still visit tokens 0..T-1."""
+    for tokens in (0, 1, 5, 128, 511, 512):
+        got = sm.dedup_chunk_tokens_receiver(tokens, 0, 1, 0)
+        assert sorted(t for t, _ in got) == list(range(tokens))
