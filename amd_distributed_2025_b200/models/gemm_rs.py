@@ -225,6 +225,9 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
     if m * n * 2 * splits_hint <= (256 << 20):
         need_stage = max(need_stage, m * n * 2 * splits_hint)
     need_counters = plan["counter_bytes"]
+    floor_mb = int(os.environ.get("B200_RS_WORKSPACE_MB", "0") or 0)
+    if floor_mb > 0 and ws > 1:
+        need_stage = max(need_stage, floor_mb << 20)
     if op is not None:
         if need_stage <= op.stage_bytes and need_counters <= op.counter_bytes:
             op._fits.add((m, n, k))
@@ -237,6 +240,22 @@ def get_op(m: int, n: int, k: int = 0, group=None, splits_hint: int = 8) -> Gemm
     op = GemmRS(need_stage, need_counters, group=group)
     op._fits.add((m, n, k))
     _OPS[key] = op
+    return op
+
+
+def reserve(shapes, group=None) -> GemmRS:
+    """Size the cached workspace once for every ``(m, n, k)`` in ``shapes`` (collective: all ranks,
+    same list).  A serving loop calls this at start-up so that no later ``custom_kernel`` call has
+    to free and re-create the workspace; ``B200_RS_WORKSPACE_MB`` sets a floor for the staging
+    capacity of one parity instead, for callers that do not know their shapes in advance."""
+    shapes = [tuple(int(v) for v in s) for s in shapes]
+    if not shapes:
+        raise ValueError("reserve() needs at least one (m, n, k) shape")
+    # largest output first: the later shapes then fit what exists, or grow it once more for counters
+    order = sorted(shapes, key=lambda s: s[0] * s[1], reverse=True)
+    op = None
+    for m, n, k in order:
+        op = get_op(m, n, k, group=group)
     return op
 
 

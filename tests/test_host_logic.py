@@ -294,3 +294,34 @@ def test_checked_layout_puts_a_guard_area_behind_every_region():
     b_off, b_len = guarded.regions["b"]
     assert a_off + a_len <= g0 < g0 + n0 <= b_off and b_off + b_len <= g1 and g1 + n1 <= guarded.total_bytes
     assert not guarded.overlaps()
+
+
+def test_gemm_rs_reserve_sizes_the_cached_workspace_once(monkeypatch):
+    """``reserve`` with the task's shapes must leave a workspace that every later ``get_op`` of those
+    shapes reuses (no free-and-recreate inside a serving loop); the env floor raises the first size."""
+    from amd_distributed_2025_b200.models import gemm_rs as g
+
+    built = []
+
+    class FakeOp:
+        def __init__(self, stage_bytes, counter_bytes, group=None):
+            self.stage_bytes, self.counter_bytes, self._fits = stage_bytes, counter_bytes, set()
+            built.append((stage_bytes, counter_bytes))
+
+        def close(self, collective=False):
+            pass
+
+    monkeypatch.setattr(g, "GemmRS", FakeOp)
+    monkeypatch.setattr(g, "_OPS", {})
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    monkeypatch.delenv("B200_RS_WORKSPACE_MB", raising=False)
+    shapes = [(256, 5120, 12800), (8192, 8192, 28672), (2048, 5120, 12800), (64, 7168, 18432)]
+    op = g.reserve(shapes)
+    n_built = len(built)
+    assert n_built <= 2 and op.stage_bytes >= 8192 * 8192 * 2
+    for m, n, k in shapes:
+        assert g.get_op(m, n, k) is op
+    assert len(built) == n_built
+    with pytest.raises(ValueError):
+        g.reserve([])
