@@ -799,6 +799,169 @@ py::dict host_moe_combine(b200::HostShmHeap& heap, std::vector<int64_t> offsets,
   return status_to_dict(w);
 }
 
+// ---- "dedup" protocol on CPU ranks ------------------------------------------------------
+
+struct HostDedupGeometry {
+  b200::HostMoeDedupLayout lay;
+  b200::HostMoeDedupShape shape;
+  int64_t ret_elem_bytes;
+};
+
+HostDedupGeometry host_dedup_geometry(const b200::HostShmHeap& heap, const std::vector<int64_t>& offsets, int64_t num_experts,
+                                      int64_t topk, int64_t hidden, int64_t max_recv, int64_t max_tokens,
+                                      at::ScalarType in_dtype, at::ScalarType out_dtype, bool partial_fp32, int64_t chunks) {
+  TORCH_CHECK(offsets.size() == 7, "expected offsets of (counts, expert_x, expert_meta, expert_y, land, tok_rec, ret)");
+  TORCH_CHECK(num_experts > 0 && num_experts % heap.world_size() == 0, "num_experts must divide by the world size");
+  TORCH_CHECK(topk > 0 && topk <= 15 && hidden > 0 && max_recv > 0 && max_tokens > 0 && max_tokens < (1 << 24), "bad MoE shape");
+  HostDedupGeometry g;
+  g.lay.counts = (uint64_t)offsets[0];
+  g.lay.expert_x = (uint64_t)offsets[1];
+  g.lay.expert_meta = (uint64_t)offsets[2];
+  g.lay.expert_y = (uint64_t)offsets[3];
+  g.lay.land = (uint64_t)offsets[4];
+  g.lay.tok_rec = (uint64_t)offsets[5];
+  g.lay.ret = (uint64_t)offsets[6];
+  g.shape.num_experts = (int)num_experts;
+  g.shape.topk = (int)topk;
+  g.shape.hidden = (int)hidden;
+  g.shape.max_recv = (int)max_recv;
+  g.shape.max_tokens = (int)max_tokens;
+  g.shape.rec_ints = (int)((1 + 2 * topk + 3) / 4 * 4);
+  g.shape.in_dtype = dtype_code(in_dtype);
+  g.shape.out_dtype = dtype_code(out_dtype);
+  g.shape.chunks = (int)std::max<int64_t>(1, std::min<int64_t>(chunks, 8));
+  g.ret_elem_bytes = partial_fp32 ? 4 : b200::host_dtype_bytes(g.shape.out_dtype);
+  const uint64_t ws = (uint64_t)heap.world_size();
+  const uint64_t cells = (uint64_t)(num_experts / heap.world_size()) * (uint64_t)max_recv;
+  const uint64_t toks = ws * (uint64_t)max_tokens;
+  const uint64_t ends[7] = {
+      g.lay.counts + ws * (uint64_t)num_experts * 4,
+      g.lay.expert_x + cells * hidden * b200::host_dtype_bytes(g.shape.in_dtype),
+      g.lay.expert_meta + cells * 5 * 4,
+      g.lay.expert_y + cells * hidden * b200::host_dtype_bytes(g.shape.out_dtype),
+      g.lay.land + toks * hidden * b200::host_dtype_bytes(g.shape.in_dtype),
+      g.lay.tok_rec + toks * g.shape.rec_ints * 4,
+      g.lay.ret + toks * hidden * (uint64_t)g.ret_elem_bytes,
+  };
+  TORCH_CHECK(g.lay.counts >= b200::kHeapHeaderBytes, "MoE regions overlap the slab header");
+  for (uint64_t e : ends) TORCH_CHECK(e <= heap.bytes(), "MoE regions do not fit the shared-memory slab");
+  return g;
+}
+
+py::tuple host_moe_dedup_dispatch(b200::HostShmHeap& heap, std::vector<int64_t> offsets, const at::Tensor& x,
+                                  const at::Tensor& indices, int64_t num_experts, int64_t max_recv, int64_t max_tokens,
+                                  at::ScalarType out_dtype, int64_t chunks, int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(x.device().is_cpu() && indices.device().is_cpu(), "host_moe_dedup_dispatch takes CPU tensors");
+  TORCH_CHECK(x.dim() == 2 && indices.dim() == 2 && x.is_contiguous(), "x [tokens, hidden] contiguous, indices [tokens, k]");
+  TORCH_CHECK(indices.size(0) <= x.size(0) && indices.size(0) <= max_tokens, "more index rows than tokens / max_tokens");
+  const HostDedupGeometry g = host_dedup_geometry(heap, offsets, num_experts, indices.size(1), x.size(1), max_recv, max_tokens,
+                                                  x.scalar_type(), out_dtype, false, chunks);
+  const at::Tensor idx = indices.to(at::kInt).contiguous();
+  const int num_tokens = (int)idx.size(0);
+  at::Tensor route = at::empty({(int64_t)num_tokens * g.shape.topk, 2}, at::TensorOptions().dtype(at::kInt));
+  at::Tensor expert_num = at::empty({g.shape.num_experts / heap.world_size()}, at::TensorOptions().dtype(at::kInt));
+  b200::StatusWord w;
+  {
+    py::gil_scoped_release release;
+    w = b200::host_moe_dedup_dispatch(heap, g.lay, g.shape, x.data_ptr(), idx.data_ptr<int32_t>(), num_tokens,
+                                      route.data_ptr<int32_t>(), expert_num.data_ptr<int32_t>(), (uint64_t)epoch,
+                                      (uint64_t)timeout_ns);
+  }
+  return py::make_tuple(status_to_dict(w), route, expert_num);
+}
+
+// Combine of the dedup protocol.  `expert_y` is any tensor of the dispatch layout (the owner
+// reduces its own expert outputs, so it need not live in the slab).  Owner side: per landed
+// (source, token) the fp32 sum over its local entries, ascending k, of weight * expert_y[row],
+// stored as ONE row into the source's return buffer.  Source side: the rows of the owners it
+// used are added in ascending rank order in fp32 and rounded once.
+py::dict host_moe_dedup_combine(b200::HostShmHeap& heap, std::vector<int64_t> offsets, int64_t num_experts, int64_t max_recv,
+                                int64_t max_tokens, at::ScalarType in_dtype, bool partial_fp32, const at::Tensor& route,
+                                const at::Tensor& weights, const at::Tensor& expert_y, at::Tensor out,
+                                int64_t dispatch_epoch, int64_t epoch, int64_t timeout_ns) {
+  TORCH_CHECK(out.device().is_cpu() && out.dim() == 2 && out.is_contiguous(), "out [tokens, hidden] contiguous on CPU");
+  TORCH_CHECK(weights.dim() == 2 && weights.scalar_type() == at::kFloat && weights.is_contiguous(),
+              "weights must be float32 [tokens, k] contiguous");
+  const int64_t num_tokens = weights.size(0), k = weights.size(1), hidden = out.size(1);
+  TORCH_CHECK(out.size(0) >= num_tokens && num_tokens <= max_tokens, "out has fewer rows than weights, or too many tokens");
+  TORCH_CHECK(route.scalar_type() == at::kInt && route.is_contiguous() && route.dim() == 2 && route.size(1) == 2 &&
+                  route.size(0) == num_tokens * k,
+              "route must be the int32 [tokens * k, 2] table returned by dispatch");
+  const HostDedupGeometry g = host_dedup_geometry(heap, offsets, num_experts, k, hidden, max_recv, max_tokens, in_dtype,
+                                                  out.scalar_type(), partial_fp32, 1);
+  const int ws = heap.world_size(), rank = heap.rank();
+  const int64_t total_rows = (int64_t)(g.shape.num_experts / ws) * g.shape.max_recv;
+  TORCH_CHECK(expert_y.device().is_cpu() && expert_y.is_contiguous() && expert_y.scalar_type() == out.scalar_type() &&
+                  expert_y.numel() == total_rows * hidden,
+              "expert_y does not have the dispatch layout / out_dtype");
+  b200::StatusWord w;
+  {
+    py::gil_scoped_release release;
+    w = b200::host_moe_dedup_send_weights(heap, g.lay, g.shape, route.data_ptr<int32_t>(), weights.data_ptr<float>(),
+                                          (int)num_tokens, (uint64_t)epoch, (uint64_t)timeout_ns);
+  }
+  if (w.code != b200::STATUS_OK) return status_to_dict(w);
+
+  // owner side: the records landed by the dispatch this combine belongs to
+  const at::ScalarType ret_dtype = partial_fp32 ? at::kFloat : out.scalar_type();
+  at::Tensor rec = host_region(heap, g.lay.tok_rec, {(int64_t)ws * max_tokens, (int64_t)g.shape.rec_ints}, at::kInt);
+  const int32_t mark = (int32_t)(uint32_t)(uint64_t)dispatch_epoch;
+  at::Tensor live = at::nonzero(rec.select(1, 0).eq((int64_t)mark)).squeeze(1);  // flat (source, token) cells
+  bool bad_row = false;
+  if (live.numel() > 0) {
+    at::Tensor mine = rec.index_select(0, live);
+    at::Tensor rows = mine.narrow(1, 1, k).to(at::kLong);
+    at::Tensor wts = mine.narrow(1, 1 + k, k).contiguous().view(at::kFloat);
+    bad_row = rows.ge(total_rows).any().item<bool>();
+    at::Tensor valid = rows.ge(0).logical_and(rows.lt(total_rows));
+    at::Tensor y2 = expert_y.view({total_rows, hidden});
+    at::Tensor acc = at::zeros({live.size(0), hidden}, at::TensorOptions().dtype(at::kFloat));
+    for (int64_t kk = 0; kk < k; ++kk) {
+      at::Tensor r = rows.select(1, kk).clamp(0, total_rows - 1);
+      at::Tensor wk = wts.select(1, kk) * valid.select(1, kk).to(at::kFloat);
+      acc.addcmul_(y2.index_select(0, r).to(at::kFloat), wk.unsqueeze(1));
+    }
+    at::Tensor any_valid = valid.any(1);
+    at::Tensor src_of = at::floor_divide(live, max_tokens);
+    at::Tensor tok_of = live - src_of * max_tokens;
+    at::Tensor partial = acc.to(ret_dtype);
+    for (int s = 0; s < ws; ++s) {
+      at::Tensor pick = at::nonzero(src_of.eq(s).logical_and(any_valid)).squeeze(1);
+      if (pick.numel() == 0) continue;
+      // row (this rank, token) of the SOURCE's return buffer
+      at::Tensor dst = at::from_blob(heap.base(s) + g.lay.ret + (uint64_t)rank * max_tokens * hidden * g.ret_elem_bytes,
+                                     {max_tokens, hidden}, at::TensorOptions().dtype(ret_dtype));
+      dst.index_copy_(0, tok_of.index_select(0, pick), partial.index_select(0, pick));
+    }
+  }
+  {
+    py::gil_scoped_release release;
+    w = b200::host_moe_dedup_return(heap, (uint64_t)epoch, (uint64_t)timeout_ns);
+  }
+  if (w.code != b200::STATUS_OK) return status_to_dict(w);
+
+  // source side: add the owners' rows, ascending rank
+  if (num_tokens > 0) {
+    at::Tensor rt = route.view({num_tokens, k, 2});
+    at::Tensor owner = rt.select(2, 0), row = rt.select(2, 1);
+    at::Tensor ret = host_region(heap, g.lay.ret, {(int64_t)ws, max_tokens, hidden}, ret_dtype);
+    at::Tensor acc = at::zeros({num_tokens, hidden}, at::TensorOptions().dtype(at::kFloat));
+    for (int d = 0; d < ws; ++d) {
+      at::Tensor used = at::nonzero(owner.eq(d).logical_and(row.ge(0)).any(1)).squeeze(1);
+      if (used.numel() == 0) continue;
+      acc.index_add_(0, used, ret.select(0, d).index_select(0, used).to(at::kFloat));
+    }
+    out.narrow(0, 0, num_tokens).copy_(acc);
+  }
+  if (bad_row) {
+    w.code = b200::STATUS_BAD_INDEX;
+    w.phase = b200::PHASE_MOE_RETURN;
+    w.peer = -1;
+    w.epoch = (uint64_t)epoch;
+  }
+  return status_to_dict(w);
+}
+
 py::tuple host_reduce_scatter(b200::HostShmHeap& heap, int64_t stage_offset, int64_t stage_bytes, const at::Tensor& partial,
                               const c10::optional<at::Tensor>& bias_once, int64_t epoch, int64_t timeout_ns) {
   TORCH_CHECK(partial.device().is_cpu() && partial.dim() == 2 && partial.is_contiguous(), "partial [M, N] contiguous on CPU");
@@ -1016,6 +1179,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("host_moe_dispatch", &host_moe_dispatch);
   m.def("host_moe_expert_scale", &host_moe_expert_scale);
   m.def("host_moe_combine", &host_moe_combine);
+  m.def("host_moe_dedup_dispatch", &host_moe_dedup_dispatch);
+  m.def("host_moe_dedup_combine", &host_moe_dedup_combine);
   m.def("host_reduce_scatter", &host_reduce_scatter);
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_expert_scale", &moe_expert_scale);

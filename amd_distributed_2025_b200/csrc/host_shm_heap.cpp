@@ -131,6 +131,11 @@ StatusWord HostShmHeap::wait(int row, int src, uint64_t epoch, uint64_t timeout_
   return w;
 }
 
+uint64_t HostShmHeap::peek(int row, int src) const {
+  if (row < 0 || row >= FLAG_ROWS || src < 0 || src >= world_) throw std::runtime_error("HostShmHeap::peek: bad row / source");
+  return flag_slot(base_[rank_], row, src)->load(std::memory_order_acquire);
+}
+
 StatusWord HostShmHeap::barrier(uint64_t epoch, uint64_t timeout_ns) {
   for (int r = 0; r < world_; ++r) signal(FLAG_BARRIER, r, epoch);
   StatusWord ok;

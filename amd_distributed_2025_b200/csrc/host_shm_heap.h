@@ -42,6 +42,9 @@ class HostShmHeap {
   // Wait until slot [row][src] of the own slab reaches `epoch`; STATUS_TIMEOUT (with phase, peer,
   // epoch, last value seen) after timeout_ns.  The first failure is also kept in last_status().
   StatusWord wait(int row, int src, uint64_t epoch, uint64_t timeout_ns, uint32_t phase);
+  // Current value of slot [row][src] of the own slab (acquire load); for words that carry data
+  // rather than a call number, read after the flag that was raised behind them.
+  uint64_t peek(int row, int src) const;
   // The device barrier's protocol on FLAG_BARRIER: signal everyone, then wait for everyone.
   StatusWord barrier(uint64_t epoch, uint64_t timeout_ns);
 

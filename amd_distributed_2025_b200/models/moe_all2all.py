@@ -368,14 +368,15 @@ def custom_kernel(data: MoEInput, backend: str = "auto", mode: Optional[str] = N
 
     ``backend``: "auto" = the fused kernels for CUDA tensors, the shared-memory operators
     (models/host_ops.py) for CPU tensors when all ranks share a machine, library collectives
-    otherwise; "shm" and "torch" force the latter two.  ``mode`` picks the GPU protocol
-    ("dedup" or "direct", default ``B200_MOE_MODE`` or "dedup")."""
+    otherwise; "shm" and "torch" force the latter two.  ``mode`` picks the protocol ("dedup" or
+    "direct"; default on GPUs ``B200_MOE_MODE`` or "dedup", on CPU ranks ``B200_HOST_MOE_MODE`` or
+    "direct")."""
     cfg, rank_data, rank, world_size = data
     x = rank_data.x
     if backend == "shm" or (backend == "auto" and not x.is_cuda and _cpu_ranks_share_a_node()):
         from . import host_ops
 
-        return host_ops.moe_custom_kernel(data)
+        return host_ops.moe_custom_kernel(data, mode=mode)
     if backend == "torch" or (backend == "auto" and not x.is_cuda):
         ata = TorchAllToAll(cfg, rank, world_size)
         n_tok, ex, em = ata.dispatch(x, rank_data.indices)

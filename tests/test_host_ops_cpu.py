@@ -72,6 +72,78 @@ def test_moe_over_shared_memory_matches_the_oracle_call_after_call(world_size, s
         assert r["cached_layers"] == 1
 
 
+def _moe_dedup_rank(rank, world_size, spec, calls):
+    _patient()
+    from amd_distributed_2025_b200.models.host_ops import HostMoEAllToAll
+
+    res = {"ok": True, "msg": "", "layout_ok": True, "layout_msg": "", "rel": 0.0}
+    cfg = _moe_inputs(spec, spec["seed"], world_size)[rank][0]
+    # every rank cuts its tokens into a different number of chunks: the owners learn it from the info word
+    layer = HostMoEAllToAll(cfg, rank, world_size, mode="dedup", chunks=1 + (rank + spec.get("chunk_shift", 0)) % 4,
+                            partial_dtype=torch.float32 if spec.get("fp32_partials") else None)
+    for call in range(calls):
+        everyone = _moe_inputs(spec, spec["seed"] + 17 * call, world_size)
+        cfg, mine, _, _ = everyone[rank]
+        n = mine.num_tokens
+        num, ex, em = layer.dispatch(mine.x, mine.indices[:n])
+        lay_ok, lay_msg = oracle.compare_dispatch_layout((num, ex, em), oracle.moe_dispatch_oracle(cfg, [e[1] for e in everyone], rank))
+        if call % 2:
+            # an expert output that does not live in the slab: the owner reduces it locally
+            ey = (ex.to(cfg.out_dtype) * (1 + rank)).clone()
+        else:
+            ey = layer.expert_scale(1 + rank)
+        y = torch.empty(n, cfg.hidden_dim, dtype=cfg.out_dtype)
+        layer.combine(y, mine.weights[:n], ey)
+        exact = oracle.moe_expected_output(cfg, mine, world_size)
+        ok, msg = oracle.check_moe_output(y, exact)
+        res["ok"] &= bool(ok)
+        res["msg"] = res["msg"] or msg
+        res["layout_ok"] &= bool(lay_ok)
+        res["layout_msg"] = res["layout_msg"] or lay_msg
+        res["rel"] = max(res["rel"], oracle.relative_error(y, exact))
+    layer.close()
+    return res
+
+
+@pytest.mark.parametrize(
+    "world_size,spec,rel",
+    [
+        (1, dict(E=8, k=2, H=64, T=16, seed=3, dtype="float32"), 1e-6),
+        (2, dict(E=16, k=2, H=256, T=32, seed=11, dtype="float32", fixed=32), 1e-6),
+        (3, dict(E=9, k=3, H=40, T=7, seed=29, dtype="float16", weights="rand", chunk_shift=2), 2e-3),
+        (4, dict(E=8, k=2, H=64, T=4, seed=1236, dtype="float16", weights="rand"), 2e-3),  # random token counts, some zero
+        (8, dict(E=64, k=6, H=512, T=48, seed=5, dtype="bfloat16", routing="zipf", fp32_partials=True), 1e-2),
+        (8, dict(E=64, k=6, H=512, T=48, seed=6, dtype="bfloat16", routing="zipf", chunk_shift=1), 2e-2),
+    ],
+)
+def test_moe_dedup_protocol_between_cpu_ranks(world_size, spec, rel):
+    """The device kernels' default protocol (one row per destination rank, records, chunk flags
+    announced through the info word, owner-side pre-reduction, one row back per owner) between
+    real processes, call after call on the same buffers."""
+    for r in run_ranks(_moe_dedup_rank, world_size, "gloo", (spec, 4), 300.0):
+        assert r["ok"], r["msg"]
+        assert r["layout_ok"], r["layout_msg"]
+        assert r["rel"] < rel
+
+
+def _modes_agree(rank, world_size):
+    _patient()
+    from amd_distributed_2025_b200.models import host_ops, moe_all2all
+
+    cfg, mine, _, _ = contract.make_moe_inputs(16, 4, 128, 16, 3, rank, world_size, device=CPU, dtype=torch.float32,
+                                               weights="softmax")
+    data = (cfg, mine, rank, world_size)
+    a = moe_all2all.custom_kernel(data, backend="shm", mode="direct")
+    b = moe_all2all.custom_kernel(data, backend="shm", mode="dedup")
+    host_ops.release()
+    return {"max_diff": float((a - b).abs().max()) if a.numel() else 0.0}
+
+
+def test_direct_and_dedup_protocols_agree_through_custom_kernel():
+    for r in run_ranks(_modes_agree, 4, "gloo", (), 300.0):
+        assert r["max_diff"] < 1e-5
+
+
 def _gemm_rank(rank, world_size, m, n, k, calls):
     _patient()
     from amd_distributed_2025_b200.models import gemm_rs, host_ops
@@ -120,7 +192,7 @@ def test_shared_memory_and_library_collective_backends_agree():
 
 # -- failure detection: a rank that stops calling ------------------------------------------
 
-def _leaver(prefix, rank, world_size, q):
+def _leaver(prefix, rank, world_size, q, mode):
     from amd_distributed_2025_b200.contract import MoEConfig
     from amd_distributed_2025_b200.models.host_ops import HostMoEAllToAll
     from amd_distributed_2025_b200.utils.status import StatusError
@@ -128,7 +200,7 @@ def _leaver(prefix, rank, world_size, q):
     torch.set_num_threads(1)
     cfg = MoEConfig(num_experts=9, experts_per_token=2, hidden_dim=32, max_num_tokens=8, in_dtype=torch.float32,
                     out_dtype=torch.float32)
-    layer = HostMoEAllToAll(cfg, rank, world_size, prefix=prefix, wait_limit_ms=300.0)
+    layer = HostMoEAllToAll(cfg, rank, world_size, prefix=prefix, wait_limit_ms=300.0, mode=mode)
     gen = torch.Generator().manual_seed(rank)
     x = torch.randn(8, 32, generator=gen)
     idx = torch.stack([torch.randperm(9, generator=gen)[:2] for _ in range(8)]).to(torch.int32)
@@ -145,11 +217,12 @@ def _leaver(prefix, rank, world_size, q):
         q.put((rank, exc.code, exc.phase, exc.status["peer"], time.perf_counter() - t0))
 
 
-def test_a_rank_that_leaves_between_steps_ends_the_others_wait_with_a_status():
+@pytest.mark.parametrize("mode", ["direct", "dedup"])
+def test_a_rank_that_leaves_between_steps_ends_the_others_wait_with_a_status(mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    prefix = f"b200_test_leave_{os.getpid()}"
-    procs = [ctx.Process(target=_leaver, args=(prefix, r, 3, q)) for r in range(3)]
+    prefix = f"b200_test_leave_{mode}_{os.getpid()}"
+    procs = [ctx.Process(target=_leaver, args=(prefix, r, 3, q, mode)) for r in range(3)]
     for p in procs:
         p.start()
     got = sorted(q.get(timeout=120) for _ in procs)
