@@ -218,3 +218,60 @@ def dedup_chunk_tokens_receiver(num_tokens: int, grid: int, chunks: int, chunk: 
             continue
         items.append((g * tpc + w * tpw + i, piece))
     return items
+
+
+def gemm_reduce_work(m: int, n: int, world_size: int, rank: int, block_n: int, grid: int, fuse_own: bool,
+                     splits: int = 1, warps_per_cta: int = 11, block_m: int = 128, epilogue_warps: int = 4):
+    """The reduction work of ``gemm_rs_kernel``'s reducer warps on one rank, as ``reduce_staged_units``
+    enumerates it: the staged m-blocks of this rank's rows, cut into units (whole tiles or 32-row
+    quarters), units into ``cuts`` runs of 8-column vectors, work items dealt to the CTAs round robin
+    (CTA ``b`` starts at ``grid - 1 - b``).  Returns ``(items, cuts, parts)`` with ``items`` a list of
+    ``(cta, row, first_vector, vectors)`` spans -- one per (unit, cut, row) -- for coverage checks."""
+    rows_per_rank = m // world_size
+    row_lo = rank * rows_per_rank
+    n_tiles = -(-n // block_n)
+    mb_lo, mb_hi = row_lo // block_m, (row_lo + rows_per_rank - 1) // block_m
+
+    def owned(mb: int) -> bool:
+        lo = mb * block_m
+        return (fuse_own and splits == 1 and lo >= row_lo and lo + block_m <= row_lo + rows_per_rank
+                and lo + block_m <= m)
+
+    lo_staged = not owned(mb_lo)
+    hi_staged = mb_hi != mb_lo and not owned(mb_hi)
+    all_staged = not (fuse_own and splits == 1)
+    n_mb = (mb_hi - mb_lo + 1) if all_staged else int(lo_staged) + int(hi_staged)
+    if n_mb == 0:
+        return [], 0, 0
+    parts = 1 if n_mb * n_tiles >= 2 * grid else epilogue_warps
+    rows_per_part = block_m // parts
+    total_units = n_tiles * n_mb * parts
+    unit_items = rows_per_part * (block_n // 8)
+    cuts = (2 * grid * warps_per_cta + total_units - 1) // total_units
+    cuts = max(1, min(cuts, unit_items // 128, 16))
+    cut_items = -(-unit_items // cuts)
+    total_work = total_units * cuts
+    items = []
+    for cta in range(grid):
+        j = grid - 1 - cta
+        while j < total_work:
+            cut, unit = j % cuts, j // cuts
+            part, rest = unit % parts, unit // parts
+            mi, nb = rest % n_mb, rest // n_mb
+            mb = mb_lo + mi if all_staged else (mb_lo if (mi == 0 and lo_staged) else mb_hi)
+            r0 = max(mb * block_m + part * rows_per_part, row_lo)
+            r1 = min(mb * block_m + (part + 1) * rows_per_part, row_lo + rows_per_rank, m)
+            if r1 > r0:
+                c0 = nb * block_n
+                c1 = min(c0 + block_n, n)
+                vec_per_row = (c1 - c0) >> 3
+                n_items = (r1 - r0) * vec_per_row
+                lo, hi = cut * cut_items, min(n_items, (cut + 1) * cut_items)
+                i = lo
+                while i < hi:
+                    row, v = divmod(i, vec_per_row)
+                    run = min(hi - i, vec_per_row - v)
+                    items.append((cta, r0 + row, (c0 >> 3) + v, run))
+                    i += run
+            j += grid
+    return items, cuts, parts

@@ -124,3 +124,47 @@ def test_dedup_small_kernel_announcement_covers_every_token():
     for tokens in (0, 1, 5, 128, 511, 512):
         got = sm.dedup_chunk_tokens_receiver(tokens, 0, 1, 0)
         assert sorted(t for t, _ in got) == list(range(tokens))
+
+
+def _task_gemm_shapes():
+    from amd_distributed_2025_b200 import contract
+
+    shapes = {(s["m"], s["n"], s["k"]) for name in ("tests", "benchmarks") for s in contract.task_specs("gemm_rs", name)}
+    return sorted(shapes | {(8192, 8192, 28672), (2048, 5120, 12800), (256, 5120, 12800)})
+
+
+@pytest.mark.parametrize("world_size", [1, 2, 4, 8])
+def test_gemm_reducers_cover_every_staged_output_vector_exactly_once(world_size):
+    """Units, cuts and the round-robin deal of ``reduce_staged_units``: for every task shape, plan
+    and grid, the staged rows of a rank (all of them above 4 ranks or with K slices, else the partly
+    owned m-blocks) are reduced once each, and every CTA gets within one work item of its share."""
+    from amd_distributed_2025_b200.ops import _ext
+
+    ext = _ext.load()
+    for m, n, k in _task_gemm_shapes():
+        if m % world_size or (k // world_size) < 64:
+            continue
+        plan = ext.gemm_rs_plan(m, n, k // world_size, world_size, 0, -1, 0)
+        bn, splits = plan["block_n"], plan["splits"]
+        fuse_own = world_size <= 4
+        rows = m // world_size
+        for grid in (148, 74, 5):
+            for rank in sorted({0, world_size // 2, world_size - 1}):
+                items, cuts, parts = sm.gemm_reduce_work(m, n, world_size, rank, bn, grid, fuse_own, splits)
+                seen = {}
+                per_cta = [0] * grid
+                for cta, row, v0, run in items:
+                    per_cta[cta] += run
+                    for v in range(v0, v0 + run):
+                        seen[(row, v)] = seen.get((row, v), 0) + 1
+                assert all(c == 1 for c in seen.values()), (m, n, k, world_size, grid, rank)
+                row_lo = rank * rows
+                expect_rows = []
+                for row in range(row_lo, row_lo + rows):
+                    lo = (row // 128) * 128
+                    tile_owned = (fuse_own and splits == 1 and lo >= row_lo and lo + 128 <= row_lo + rows and lo + 128 <= m)
+                    if not tile_owned:
+                        expect_rows.append(row)
+                assert len(seen) == len(expect_rows) * (n // 8), (m, n, k, world_size, grid, rank, cuts, parts)
+                assert {r for r, _ in seen} == set(expect_rows)
+                assert 1 <= cuts <= 16 or not items
