@@ -35,6 +35,7 @@ import os
 from typing import Dict, Optional, Tuple
 
 import torch
+import torch.distributed as dist
 
 from ..contract import META_DIM, MoEConfig, MoEInput
 from ..parallel.baseline_nccl import TorchAllToAll
@@ -133,6 +134,7 @@ class MoEAllToAll:
         self._route = torch.full((n_max, 2), -1, **i32)
         self.expert_num_tokens = torch.zeros(self.num_local_experts, **i32)
         self._num_tokens = 0
+        self._dispatch_pending = False  # a dedup dispatch whose combine has not run yet
         self._off_counts = self.ws.offset("counts")
         self._off_expert_x = self.ws.offset("expert_x")
         self._off_expert_meta = self.ws.offset("expert_meta")
@@ -160,6 +162,18 @@ class MoEAllToAll:
         if self.monitor is not None:
             self.monitor.beat()
             self.monitor.assert_all_alive()
+
+    def _quiesce_before_second_dispatch(self) -> None:
+        """The dedup buffers are reused without a barrier because calls alternate dispatch and
+        combine: a rank enters the next dispatch only after every owner's return flag, i.e. after
+        every owner has read what the next dispatch overwrites.  A dispatch that follows a dispatch
+        has no such flag behind it (a fast sender could land new rows while a slow owner still
+        replicates the previous ones), so this unusual sequence pays a device synchronisation and
+        a host barrier instead."""
+        if self._dispatch_pending and self.world_size > 1:
+            torch.cuda.synchronize(self.device)
+            if dist.is_available() and dist.is_initialized():
+                dist.barrier(group=self.group)
 
     def enable_trace(self, on: bool = True) -> None:
         """Record ``globaltimer`` phase stamps (ns) of the next dedup calls: ``trace[0]`` dispatch =
@@ -190,6 +204,8 @@ class MoEAllToAll:
         idx = indices.to(torch.int32).contiguous()
         self._num_tokens = x.shape[0]
         if self.engine is not None:
+            self._quiesce_before_second_dispatch()
+            self._dispatch_pending = True
             if self.engine.dispatch(x, idx):
                 self.ws.check()
             return self.expert_num_tokens, self.expert_x, self.expert_meta
@@ -249,6 +265,7 @@ class MoEAllToAll:
             target = out_tokens
             if accumulate or not out_tokens.is_contiguous() or out_tokens.dtype != self.cfg.out_dtype:
                 target = torch.empty((max(n, 1), self.cfg.hidden_dim), dtype=self.cfg.out_dtype, device=out_tokens.device)
+            self._dispatch_pending = False
             if self.engine.combine(target, weights.to(torch.float32).contiguous(), expert_y.contiguous()):
                 self.ws.check()
             if target is not out_tokens:
@@ -302,6 +319,8 @@ class MoEAllToAll:
         self._num_tokens = x.shape[0]
         out = torch.empty((x.shape[0], cfg.hidden_dim), dtype=cfg.out_dtype, device=x.device)
         if self.engine is not None:
+            self._quiesce_before_second_dispatch()
+            self._dispatch_pending = False
             if self.engine.forward(x, idx, w, out, float(scale)):
                 self.ws.check()  # an earlier kernel recorded a failure: raise it
             return out

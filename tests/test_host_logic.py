@@ -325,3 +325,43 @@ def test_gemm_rs_reserve_sizes_the_cached_workspace_once(monkeypatch):
     assert len(built) == n_built
     with pytest.raises(ValueError):
         g.reserve([])
+
+
+def test_second_dedup_dispatch_without_combine_waits_for_all_ranks(monkeypatch):
+    """Dispatch after dispatch has no return flag behind it, so the layer must synchronise and meet
+    the other ranks on the host first; the usual dispatch -> combine -> dispatch order must not."""
+    from amd_distributed_2025_b200.models import moe_all2all as m
+
+    calls = []
+
+    class Engine:
+        def dispatch(self, x, idx):
+            calls.append("dispatch")
+            return 0
+
+        def combine(self, out, w, y):
+            calls.append("combine")
+            return 0
+
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: calls.append("sync"))
+    monkeypatch.setattr(m.dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(m.dist, "barrier", lambda group=None: calls.append("barrier"))
+    layer = m.MoEAllToAll.__new__(m.MoEAllToAll)
+    cfg = contract.MoEConfig(num_experts=8, experts_per_token=2, hidden_dim=16, max_num_tokens=4,
+                             in_dtype=torch.float32, out_dtype=torch.float32)
+    layer.cfg, layer.world_size, layer.rank, layer.group, layer.device = cfg, 2, 0, None, torch.device("cpu")
+    layer.engine, layer.monitor, layer._dispatch_pending, layer._num_tokens = Engine(), None, False, 0
+    layer.ws = type("W", (), {"check": lambda self, sync=True: None})()
+    layer.expert_num_tokens = layer.expert_x = layer.expert_meta = None
+    layer.expert_y = torch.zeros(4, 8, 16)
+    x, idx, w = torch.zeros(4, 16), torch.zeros(4, 2, dtype=torch.int32), torch.zeros(4, 2)
+    y = torch.zeros(4, 16)
+    layer.dispatch(x, idx)
+    layer.combine(y, w, None, layer.expert_y, None)
+    layer.dispatch(x, idx)
+    assert calls == ["dispatch", "combine", "dispatch"]
+    layer.dispatch(x, idx)  # no combine in between
+    assert calls[3:] == ["sync", "barrier", "dispatch"]
+    layer.world_size = 1
+    layer.dispatch(x, idx)  # a single rank has no peers to wait for
+    assert calls[6:] == ["dispatch"]
