@@ -366,6 +366,10 @@ class MoeDedupEngine {
     const int64_t want = ((int64_t)ws * std::max<int64_t>(T, 1) * p.pieces + 7) / 8;
     const int grid = (int)std::max<int64_t>(std::min<int64_t>(combine_blocks_, want), 1);
     cuda_check(b200::launch_moe_dedup_combine(p, grid, at::cuda::getCurrentCUDAStream()), "moe_dedup_combine launch");
+    // A further combine of the same dispatch (other weights, another expert output) sends its own
+    // weights: that exchange is also the rendezvous which keeps an owner from pushing new partial
+    // rows while a source still adds up the previous ones.
+    weights_sent_ = false;
     return 0;
   }
 
