@@ -144,6 +144,35 @@ def test_direct_and_dedup_protocols_agree_through_custom_kernel():
         assert r["max_diff"] < 1e-5
 
 
+def _some_ranks_without_tokens(rank, world_size):
+    _patient()
+    from amd_distributed_2025_b200.models.host_ops import HostMoEAllToAll
+
+    cfg = contract.MoEConfig(num_experts=8, experts_per_token=2, hidden_dim=32, max_num_tokens=8, in_dtype=torch.float32,
+                             out_dtype=torch.float32)
+    worst = 0.0
+    for mode in ("direct", "dedup"):
+        layer = HostMoEAllToAll(cfg, rank, world_size, mode=mode, chunks=3)
+        for call in range(4):
+            gen = torch.Generator().manual_seed(100 * call + rank)
+            tokens = 0 if (rank + call) % 2 == 0 else 5  # every other rank sends nothing, alternating per call
+            x = torch.randn(tokens, 32, generator=gen)
+            idx = (torch.stack([torch.randperm(8, generator=gen)[:2] for _ in range(tokens)]).to(torch.int32)
+                   if tokens else torch.zeros(0, 2, dtype=torch.int32))
+            w = torch.rand(tokens, 2, generator=gen)
+            y = layer.forward(x, idx, w, 2.0)  # the same scale on every owner: y = 2 x sum_k w_k
+            if tokens:
+                worst = max(worst, float((y - 2.0 * x * w.sum(1, keepdim=True)).abs().max()))
+            assert list(y.shape) == [tokens, 32]
+        layer.close()
+    return {"err": worst}
+
+
+def test_ranks_without_tokens_still_take_part_in_every_exchange():
+    for r in run_ranks(_some_ranks_without_tokens, 4, "gloo", (), 300.0):
+        assert r["err"] < 1e-5
+
+
 def _gemm_rank(rank, world_size, m, n, k, calls):
     _patient()
     from amd_distributed_2025_b200.models import gemm_rs, host_ops
