@@ -173,6 +173,47 @@ def test_ranks_without_tokens_still_take_part_in_every_exchange():
         assert r["err"] < 1e-5
 
 
+def _many_calls(rank, world_size, calls):
+    _patient()
+    from amd_distributed_2025_b200.models.host_ops import HostGemmRS, HostMoEAllToAll
+
+    torch.set_num_threads(1)
+    cfg = contract.MoEConfig(num_experts=8, experts_per_token=3, hidden_dim=24, max_num_tokens=6, in_dtype=torch.float32,
+                             out_dtype=torch.float32)
+    layers = [HostMoEAllToAll(cfg, rank, world_size, mode="direct"),
+              HostMoEAllToAll(cfg, rank, world_size, mode="dedup", chunks=2)]
+    op = HostGemmRS(world_size * 8 * 16 * 4, rank, world_size)
+    worst = 0.0
+    for call in range(calls):
+        gen = torch.Generator().manual_seed(7919 * call + rank)
+        tokens = int(torch.randint(0, 7, (1,), generator=gen))
+        x = torch.randn(tokens, 24, generator=gen)
+        idx = (torch.stack([torch.randperm(8, generator=gen)[:3] for _ in range(tokens)]).to(torch.int32)
+               if tokens else torch.zeros(0, 3, dtype=torch.int32))
+        w = torch.rand(tokens, 3, generator=gen)
+        y = layers[call % 2].forward(x, idx, w, 1.5)
+        if tokens:
+            worst = max(worst, float((y - 1.5 * x * w.sum(1, keepdim=True)).abs().max()))
+        # a reduce-scatter in between, its shape changing from call to call (same two parities)
+        m = world_size * (1 + call % 8)
+        a = torch.full((m, 4), float(rank + 1))
+        wt = torch.ones(16, 4)
+        out = op(a, wt)
+        want = 4.0 * sum(range(1, world_size + 1))
+        worst = max(worst, float((out - want).abs().max()))
+    for layer in layers:
+        layer.close()
+    op.close()
+    return {"err": worst}
+
+
+def test_hundreds_of_back_to_back_calls_with_changing_sizes_need_no_barrier():
+    """Flag epochs, chunk flag values and the two staging parities over 300 calls whose token counts
+    (zero included) and row counts change every call, three operators interleaved on every rank."""
+    for r in run_ranks(_many_calls, 4, "gloo", (300,), 600.0):
+        assert r["err"] < 1e-4
+
+
 def _gemm_rank(rank, world_size, m, n, k, calls):
     _patient()
     from amd_distributed_2025_b200.models import gemm_rs, host_ops
