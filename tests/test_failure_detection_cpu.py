@@ -5,7 +5,6 @@ import multiprocessing as mp
 import os
 import time
 
-import pytest
 import torch
 import torch.distributed as dist
 
