@@ -295,7 +295,11 @@ class MoeDedupEngine {
     // (pays when a rank's inbound link, not its memory, sets the pace: measured a loss on 2 ranks)
     p.chunks = (!small && ws >= chunk_min_ranks && T * H_ * elem_ >= chunk_min_bytes) ? (int)chunks : 1;
     p.pieces = pieces_for((int)T, max_blocks, 1);
-    p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, 32);
+    // Replication goes source by source, so one loop has (tokens of one source's chunk) x pieces items.
+    // Measured: on 8 ranks one piece per row (a hot owner's 1024 live rows per loop already fill the
+    // grid's warps once, and every further piece costs another dependent record load); on fewer
+    // ranks the finer split, which evens out the warps' shares.
+    p.rep_pieces = pieces_for((int)std::max<int64_t>(T / p.chunks, 1), max_blocks, ws >= 8 ? 12 : 32);
     p.bulk_landing = bulk;
     p.fuse_scale = fuse_scale ? 1 : 0;
     p.scale = (float)scale;
