@@ -134,7 +134,7 @@ class MoEAllToAll:
         self._route = torch.full((n_max, 2), -1, **i32)
         self.expert_num_tokens = torch.zeros(self.num_local_experts, **i32)
         self._num_tokens = 0
-        self._dispatch_pending = False  # a dedup dispatch whose combine has not run yet
+        self._dispatch_pending = False  # a dispatch whose combine has not run yet
         self._off_counts = self.ws.offset("counts")
         self._off_expert_x = self.ws.offset("expert_x")
         self._off_expert_meta = self.ws.offset("expert_meta")
@@ -164,12 +164,13 @@ class MoEAllToAll:
             self.monitor.assert_all_alive()
 
     def _quiesce_before_second_dispatch(self) -> None:
-        """The dedup buffers are reused without a barrier because calls alternate dispatch and
-        combine: a rank enters the next dispatch only after every owner's return flag, i.e. after
-        every owner has read what the next dispatch overwrites.  A dispatch that follows a dispatch
-        has no such flag behind it (a fast sender could land new rows while a slow owner still
-        replicates the previous ones), so this unusual sequence pays a device synchronisation and
-        a host barrier instead."""
+        """The buffers are reused without a barrier because calls alternate dispatch and combine:
+        a rank enters the next dispatch only after a combine in which every rank took part, i.e.
+        after every owner has read (and its caller has used) what the next dispatch overwrites.  A
+        dispatch that follows a dispatch has no such rendezvous behind it -- a fast sender could
+        land new rows while a slow owner still replicates the previous ones ("dedup"), or overwrite
+        ``expert_x`` rows that the owner's caller still reads ("direct") -- so this unusual
+        sequence pays a device synchronisation and a host barrier instead."""
         if self._dispatch_pending and self.world_size > 1:
             torch.cuda.synchronize(self.device)
             if dist.is_available() and dist.is_initialized():
@@ -203,9 +204,9 @@ class MoEAllToAll:
         x = dp_x.contiguous()
         idx = indices.to(torch.int32).contiguous()
         self._num_tokens = x.shape[0]
+        self._quiesce_before_second_dispatch()
+        self._dispatch_pending = True
         if self.engine is not None:
-            self._quiesce_before_second_dispatch()
-            self._dispatch_pending = True
             if self.engine.dispatch(x, idx):
                 self.ws.check()
             return self.expert_num_tokens, self.expert_x, self.expert_meta
@@ -258,6 +259,7 @@ class MoEAllToAll:
         if n != self._num_tokens:
             raise ValueError("num_tokens differs from the preceding dispatch")
         self._guard()
+        self._dispatch_pending = False
         if self.engine is not None:
             # the owner reduces its own expert outputs, so any local tensor of the dispatch layout will do
             if expert_y.shape != self.expert_y.shape or expert_y.dtype != self.expert_y.dtype:
@@ -265,7 +267,6 @@ class MoEAllToAll:
             target = out_tokens
             if accumulate or not out_tokens.is_contiguous() or out_tokens.dtype != self.cfg.out_dtype:
                 target = torch.empty((max(n, 1), self.cfg.hidden_dim), dtype=self.cfg.out_dtype, device=out_tokens.device)
-            self._dispatch_pending = False
             if self.engine.combine(target, weights.to(torch.float32).contiguous(), expert_y.contiguous()):
                 self.ws.check()
             if target is not out_tokens:
@@ -318,9 +319,9 @@ class MoEAllToAll:
         w = weights if (weights.dtype == torch.float32 and weights.is_contiguous()) else weights.to(torch.float32).contiguous()
         self._num_tokens = x.shape[0]
         out = torch.empty((x.shape[0], cfg.hidden_dim), dtype=cfg.out_dtype, device=x.device)
+        self._quiesce_before_second_dispatch()
+        self._dispatch_pending = False
         if self.engine is not None:
-            self._quiesce_before_second_dispatch()
-            self._dispatch_pending = False
             if self.engine.forward(x, idx, w, out, float(scale)):
                 self.ws.check()  # an earlier kernel recorded a failure: raise it
             return out
