@@ -96,6 +96,9 @@ class HostMoEAllToAll:
         if indices.shape[0] > cfg.max_num_tokens:
             raise ValueError(f"{indices.shape[0]} tokens exceed max_num_tokens={cfg.max_num_tokens}")
         _check_peers(self.monitor)
+        # No guard is needed for a dispatch that follows a dispatch: in both protocols a rank stores
+        # nothing on a peer before it has every rank's counts of the new call, and a rank publishes
+        # those only when its caller has entered the new call, i.e. is done with the old buffers.
         if self.mode == "dedup":
             self._dispatch_epoch = self.ws.next_epoch("moe_dispatch")
             status, route, num = self.ext.host_moe_dedup_dispatch(

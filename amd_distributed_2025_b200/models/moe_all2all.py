@@ -164,14 +164,16 @@ class MoEAllToAll:
             self.monitor.assert_all_alive()
 
     def _quiesce_before_second_dispatch(self) -> None:
-        """The buffers are reused without a barrier because calls alternate dispatch and combine:
-        a rank enters the next dispatch only after a combine in which every rank took part, i.e.
-        after every owner has read (and its caller has used) what the next dispatch overwrites.  A
-        dispatch that follows a dispatch has no such rendezvous behind it -- a fast sender could
-        land new rows while a slow owner still replicates the previous ones ("dedup"), or overwrite
-        ``expert_x`` rows that the owner's caller still reads ("direct") -- so this unusual
-        sequence pays a device synchronisation and a host barrier instead."""
-        if self._dispatch_pending and self.world_size > 1:
+        """The dedup buffers are reused without a barrier because calls alternate dispatch and
+        combine: a rank enters the next dispatch only after a combine in which every rank took
+        part, i.e. after every owner has read what the next dispatch overwrites.  A dispatch that
+        follows a dispatch has no such rendezvous behind it: the small kernel sends its rows before
+        it has the peers' counts, so a fast sender could land new rows while a slow owner still
+        replicates the previous ones.  This unusual sequence pays a device synchronisation and a
+        host barrier instead.  (The "direct" kernels and the large dedup kernel store nothing on a
+        peer before they have every rank's counts of the new call, which a rank publishes only
+        once it has entered that call: they need no guard.)"""
+        if self._dispatch_pending and self.world_size > 1 and self.engine is not None:
             torch.cuda.synchronize(self.device)
             if dist.is_available() and dist.is_initialized():
                 dist.barrier(group=self.group)

@@ -316,3 +316,33 @@ def test_single_process_world_of_one_needs_no_process_group():
     ok, msg = oracle.check_gemm_rs_output(out, oracle.gemm_rs_fused_rounding([a], [w], b, 0))
     assert ok, msg
     host_ops.release()
+
+
+def _dispatch_twice(rank, world_size, mode):
+    _patient()
+    import time as _time
+
+    from amd_distributed_2025_b200.models.host_ops import HostMoEAllToAll
+
+    cfg = contract.MoEConfig(num_experts=4, experts_per_token=2, hidden_dim=16, max_num_tokens=4, in_dtype=torch.float32,
+                             out_dtype=torch.float32)
+    layer = HostMoEAllToAll(cfg, rank, world_size, mode=mode)
+    idx = torch.tensor([[0, 2], [1, 3], [2, 0], [3, 1]], dtype=torch.int32)
+    first = torch.full((4, 16), 1.0 + rank)
+    second = torch.full((4, 16), 100.0 + rank)
+    num, ex, _ = layer.dispatch(first, idx)
+    if rank == 0:
+        _time.sleep(0.5)  # this rank's caller is slow to look at what it received ...
+    seen = ex.clone()     # ... and must still find the FIRST dispatch's rows, whatever the others do meanwhile
+    layer.dispatch(second, idx)
+    after = layer.expert_x.clone()
+    layer.close()
+    return {"first_ok": bool((seen[:, :4] < 50.0).all()), "second_ok": bool((after[:, :4] > 50.0).all()),
+            "rows": int(num.sum())}
+
+
+@pytest.mark.parametrize("mode", ["direct", "dedup"])
+def test_a_second_dispatch_never_overwrites_rows_a_slow_rank_still_reads(mode):
+    for r in run_ranks(_dispatch_twice, 2, "gloo", (mode,), 300.0):
+        assert r["rows"] == 8  # 4 tokens x 2 entries x 2 ranks over 4 experts: 4 rows per expert, 2 experts per rank
+        assert r["first_ok"] and r["second_ok"]
