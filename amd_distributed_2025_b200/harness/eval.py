@@ -69,6 +69,15 @@ def _worker(rank: int, world_size: int, backend: str, port: int, fn: Callable, a
         out["ok"] = True
     except Exception:  # noqa: BLE001 - the parent re-raises with the traceback text
         out["error"] = traceback.format_exc()
+        if backend == "nccl" and dist.is_initialized():
+            # A GPU rank that failed still takes its workspaces down together with the others (they
+            # reach their own teardown at the end of ``fn`` or after their bounded waits expire): no
+            # rank may leave while a peer maps its slab, or while its memory is bound to an NVLink
+            # multicast object that a peer can still read through.
+            try:
+                release_workspaces()
+            except Exception:  # noqa: BLE001
+                out["error"] += "\n(teardown after the failure also failed)\n" + traceback.format_exc()
     finally:
         with open(os.path.join(result_dir, f"rank{rank}.json"), "w", encoding="utf-8") as fh:
             json.dump(out, fh)

@@ -384,5 +384,25 @@ def main() -> int:
     return 0
 
 
+def _release_after_failure() -> None:
+    """A rank that failed still takes its cached workspaces down together with the others before
+    it exits (they fail too, at the latest when their bounded waits expire): no slab is freed
+    while a peer maps it, no memory leaves an NVLink multicast object that a peer can still read."""
+    try:
+        from amd_distributed_2025_b200.models import gemm_rs, moe_all2all
+
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        moe_all2all.release_layers()
+        gemm_rs.release_ops()
+    except Exception:  # noqa: BLE001 - the original failure is the one to report
+        pass
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    try:
+        code = main()
+    except Exception:
+        _release_after_failure()
+        raise
+    sys.exit(code)

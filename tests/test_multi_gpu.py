@@ -239,17 +239,20 @@ def _mcast_rank(rank, world_size):
         ws = McastWorkspace(4 << 20, rank=rank, world_size=world_size)
     except RuntimeError as exc:
         return {"available": False, "why": str(exc)}
-    n = 1 << 16
-    ws.view(0, (n,), torch.bfloat16).fill_(float(rank + 1))
-    torch.cuda.synchronize()
-    torch.distributed.barrier()
-    out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
-    ws.region.reduce_selftest(0, out)
-    torch.cuda.synchronize()
-    want = float(world_size * (world_size + 1) // 2)
-    good = bool((out.float() == want).all())
-    torch.distributed.barrier()
-    ws.close(collective=True)
+    try:
+        n = 1 << 16
+        ws.view(0, (n,), torch.bfloat16).fill_(float(rank + 1))
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+        ws.region.reduce_selftest(0, out)
+        torch.cuda.synchronize()
+        want = float(world_size * (world_size + 1) // 2)
+        good = bool((out.float() == want).all())
+        torch.distributed.barrier()
+    finally:
+        # whatever happened above: no rank leaves while its memory is bound to the multicast object
+        ws.close(collective=True)
     return {"available": True, "ok": good, "got": float(out[0]), "want": want}
 
 
