@@ -165,10 +165,25 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     print(json.dumps(out), flush=True)
     if ws > 1:
+        _release()  # collective: nobody exits while a peer maps its slab or its memory is bound to a multicast object
         dist.barrier()
         dist.destroy_process_group()
     return 0
 
 
+def _release() -> None:
+    from .eval import release_workspaces
+
+    release_workspaces()
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    try:
+        code = main()
+    except Exception:
+        try:
+            _release()  # a rank that failed still takes its workspaces down together with the others
+        except Exception:  # noqa: BLE001 - the original failure is the one to report
+            pass
+        raise
+    sys.exit(code)
